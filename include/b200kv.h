@@ -1,0 +1,171 @@
+/*
+ * b200kv — C ABI of the paged-KV attention path for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and strides (in
+ * ELEMENTS of the pointed-to type unless a name ends in _bytes) and a CUDA
+ * stream passed as void* (a cudaStream_t; NULL = the legacy default stream).
+ * Nothing here allocates or frees device memory, synchronises the device, or
+ * keeps a pointer after the call returns (the one exception is documented on
+ * the entry point itself).  All launches are asynchronous on `stream`.
+ *
+ * Return value: 0 on success, otherwise one of the B200KV_E* codes below;
+ * b200kv_strerror() turns a code into text.  Arguments are validated on the
+ * host BEFORE anything is launched, so a non-zero return means nothing ran.
+ *
+ * Device-side index checks: kernels bounds-check every slot / page id they
+ * read from device memory.  An out-of-range index is never dereferenced; the
+ * access is skipped and, when `status` is not NULL, the first offending code
+ * is recorded in *status (a device int32 the caller zeroes beforehand and may
+ * read back whenever it is willing to synchronise).
+ *
+ * The reference project (lite_llama, Python + Triton-Ascend) has no native
+ * interface; each function below names the reference Python operator whose
+ * device work it replaces, as file:line inside that project.
+ */
+#ifndef B200KV_H_
+#define B200KV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200KV_VERSION 100
+
+/* ---- host-side return codes ------------------------------------------- */
+#define B200KV_OK              0
+#define B200KV_EINVAL          1  /* NULL pointer, negative size, bad enum      */
+#define B200KV_EUNSUPPORTED    2  /* head_dim / page_size / group size not built */
+#define B200KV_EALIGN          3  /* pointer or stride not 16-byte aligned       */
+#define B200KV_EWORKSPACE      4  /* workspace too small                         */
+#define B200KV_ECUDA           5  /* a CUDA runtime call failed (see last error) */
+#define B200KV_ETOOLARGE       6  /* size beyond a documented fixed maximum      */
+
+/* ---- device-side status codes written to *status ---------------------- */
+#define B200KV_DEV_OK            0
+#define B200KV_DEV_BAD_SLOT      101  /* slot_mapping entry outside the pool     */
+#define B200KV_DEV_BAD_PAGE      102  /* table entry outside the pool            */
+#define B200KV_DEV_BAD_LENGTH    103  /* negative length or length > table width */
+#define B200KV_DEV_WAIT_TIMEOUT  104  /* a bounded device-side wait ran out      */
+
+/* ---- table kinds ------------------------------------------------------- */
+/* BLOCK: table[row][p] = physical page id of logical page p.
+ * TOKEN: table[row][t] = physical token slot of logical token t, where the
+ *        page_size slots of one page are consecutive and page-aligned (what
+ *        the reference's PagedReqTokensManager writes,
+ *        lite_llama/executor/paged_attention.py:116-147,346-358).  Only
+ *        entries at t % page_size == 0 are read. */
+#define B200KV_TABLE_BLOCK 0
+#define B200KV_TABLE_TOKEN 1
+
+int b200kv_version(void);
+const char* b200kv_strerror(int code);
+/* Text of the last CUDA error seen by this library on the calling thread. */
+const char* b200kv_last_cuda_error(void);
+
+/*
+ * KV append: pool[slots[i], r, :] = kv_values[i, r, :] for r in [0, n_rows).
+ * Replaces update_kv_buffer (lite_llama/kernels/update_kv_buffer.py:47-81,
+ * kernel :7-43).  Pure 16-byte-vector copy, bit-exact.
+ *   kv_values  fp16 [n_tokens, n_rows, head_dim], row-contiguous inside a token,
+ *              token stride src_tok_stride
+ *   slots      int32 [n_tokens]  (the slot_mapping / cur_select_index)
+ *   pool       fp16 [pool_tokens, n_rows, head_dim], token stride pool_tok_stride
+ *   n_rows     2 * kv_heads (K heads first, then V heads)
+ * n_tokens == 0 is a no-op.  Duplicate slots in one call race (last writer
+ * wins, as in the reference).
+ */
+int b200kv_kv_append(const void* kv_values, int64_t n_tokens, int64_t src_tok_stride,
+                     const int32_t* slots,
+                     void* pool, int64_t pool_tokens, int64_t pool_tok_stride,
+                     int n_rows, int head_dim,
+                     int32_t* status, void* stream);
+
+/*
+ * Same scatter with K and V given separately ([n_tokens, kv_heads, head_dim]
+ * each), so the caller need not materialise torch.cat([xk, xv], dim=-2)
+ * (lite_llama/models/qwen3.py:29,62) first.
+ */
+int b200kv_kv_append_split(const void* k_values, const void* v_values,
+                           int64_t n_tokens, int64_t k_tok_stride, int64_t v_tok_stride,
+                           const int32_t* slots,
+                           void* pool, int64_t pool_tokens, int64_t pool_tok_stride,
+                           int kv_heads, int head_dim,
+                           int32_t* status, void* stream);
+
+/*
+ * Bytes of scratch that b200kv_paged_decode needs for a batch of `batch`
+ * sequences on the CURRENT device (split-KV partial outputs and their
+ * log-sum-exp).  Depends on the device's SM count.  Returns 0 on bad input.
+ */
+size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim);
+
+/*
+ * Paged flash-decoding: one query token per sequence attends to that
+ * sequence's whole paged context.  Replaces flash_decoding
+ * (lite_llama/kernels/flashdecoding.py:295-342; stage 1 :6-138, stage 2
+ * :199-267).  Two launches: a persistent split-KV kernel in which each CTA
+ * serves one KV head together with its whole GQA query group, then a
+ * log-sum-exp merge of the split partials.
+ *   q          fp16 [batch, q_heads, head_dim]; strides q_stride_b, q_stride_h
+ *   k_base     fp16 K view of the pool, element (t, h, d) at
+ *              k_base + t*kv_tok_stride + h*kv_head_stride + d
+ *   v_base     likewise for V (same strides)
+ *   pool_tokens number of token slots addressable from k_base / v_base
+ *   table      int32, row stride table_row_stride, kind B200KV_TABLE_*
+ *   row_ids    int32 [batch] table row of each sequence, or NULL = 0..batch-1
+ *              (the reference indexes rows by batch position,
+ *              lite_llama/kernels/flashdecoding.py:48,85)
+ *   seq_lens   int32 or int64 [batch] (seq_lens_i64 selects); length 0 gives
+ *              an all-zero output row
+ *   scale      natural softmax scale (1/sqrt(head_dim)); softmax is base e
+ *   max_seq_len host upper bound of the lengths (sizes the launch only)
+ *   out        fp16 [batch, q_heads, head_dim]; strides out_stride_b, out_stride_h
+ * Supported: head_dim 128, page_size 16, q_heads/kv_heads in [1,16], batch <= 4096.
+ */
+int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                        const void* k_base, const void* v_base,
+                        int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
+                        const int32_t* table, int64_t table_row_stride, int table_kind,
+                        const int32_t* row_ids,
+                        const void* seq_lens, int seq_lens_i64,
+                        int batch, int q_heads, int kv_heads, int head_dim, int page_size,
+                        float scale, int64_t max_seq_len,
+                        void* workspace, size_t workspace_bytes,
+                        void* out, int64_t out_stride_b, int64_t out_stride_h,
+                        int32_t* status, void* stream);
+
+/*
+ * Packed no-pad causal prefill over paged KV with history: query row i of
+ * request r sits at logical position ctx_r + i and sees keys 0..ctx_r+i of
+ * that request's table row.  Replaces paged_chunk_flash_attention
+ * (lite_llama/kernels/paged_chunk_flashattention.py:227-327, kernel :58-176,
+ * torch statement :179-222) and, with ctx = 0, flash_attention2_no_pad
+ * (lite_llama/kernels/flashattention2_nopad.py:171-221) once the chunk's own
+ * K/V have been appended to the pool.  Tensor-core (tcgen05 / TMEM) kernel.
+ *   q          fp16 [total_q, q_heads, head_dim] packed; strides q_stride_t, q_stride_h
+ *   req_ids    int32 [batch] table row of each request, or NULL = 0..batch-1
+ *   q_start    int32 [batch] first packed row of each request
+ *   ctx_lens, q_lens  int32 or int64 [batch] (lens_i64 selects)
+ *   max_q_len  host upper bound of q_lens (sizes the launch only)
+ *   scale_log2 softmax scale already multiplied by log2(e), as the reference's
+ *              callers pass it (lite_llama/models/qwen3.py:296)
+ */
+int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h,
+                         const void* k_base, const void* v_base,
+                         int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
+                         const int32_t* table, int64_t table_row_stride, int table_kind,
+                         const int32_t* req_ids, const int32_t* q_start,
+                         const void* ctx_lens, const void* q_lens, int lens_i64,
+                         int batch, int64_t total_q, int64_t max_q_len,
+                         int q_heads, int kv_heads, int head_dim, int page_size,
+                         float scale_log2,
+                         void* out, int64_t out_stride_t, int64_t out_stride_h,
+                         int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200KV_H_ */

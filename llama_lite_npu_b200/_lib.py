@@ -1,0 +1,106 @@
+"""ctypes binding of libb200kv.so — the only route from Python to the CUDA kernels.
+
+There is deliberately no fallback: if the shared library is missing or a symbol
+cannot be resolved, importing this module's :func:`lib` raises, and every
+operator in :mod:`llama_lite_npu_b200.kernels` fails with it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libb200kv.so"
+
+# name -> (restype, argtypes); mirrors include/b200kv.h one to one.
+_SIGNATURES = {
+    "b200kv_version": (c_int, []),
+    "b200kv_strerror": (c_char_p, [c_int]),
+    "b200kv_last_cuda_error": (c_char_p, []),
+    "b200kv_kv_append": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int,
+         c_void_p, c_void_p],
+    ),
+    "b200kv_kv_append_split": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
+         c_int, c_int, c_void_p, c_void_p],
+    ),
+    "b200kv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "b200kv_paged_decode": (
+        c_int,
+        [c_void_p, c_int64, c_int64,             # q
+         c_void_p, c_void_p, c_int64, c_int64, c_int64,   # k, v, strides, pool_tokens
+         c_void_p, c_int64, c_int,               # table
+         c_void_p,                               # row_ids
+         c_void_p, c_int,                        # seq_lens
+         c_int, c_int, c_int, c_int, c_int,      # batch, heads, dims
+         c_float, c_int64,                       # scale, max_seq_len
+         c_void_p, c_size_t,                     # workspace
+         c_void_p, c_int64, c_int64,             # out
+         c_void_p, c_void_p],                    # status, stream
+    ),
+    "b200kv_paged_prefill": (
+        c_int,
+        [c_void_p, c_int64, c_int64,
+         c_void_p, c_void_p, c_int64, c_int64, c_int64,
+         c_void_p, c_int64, c_int,
+         c_void_p, c_void_p,
+         c_void_p, c_void_p, c_int,
+         c_int, c_int64, c_int64,
+         c_int, c_int, c_int, c_int,
+         c_float,
+         c_void_p, c_int64, c_int64,
+         c_void_p, c_void_p],
+    ),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+_lib = None
+
+
+class B200KVError(RuntimeError):
+    """A libb200kv entry point returned a non-zero code."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"b200kv error {code}: {message}")
+        self.code = code
+
+
+def lib() -> ctypes.CDLL:
+    """Load (once) and return the shared library with typed entry points."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m llama_lite_npu_b200.build` "
+            "(there is no CPU or PyTorch fallback for the b200kv operators)"
+        )
+    handle = ctypes.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(handle, name)  # AttributeError if the symbol is missing
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = handle
+    return handle
+
+
+def check(code: int) -> None:
+    """Raise for a non-zero return code of an entry point."""
+    if code == 0:
+        return
+    handle = lib()
+    msg = handle.b200kv_strerror(code).decode()
+    if code == 5:
+        msg += " — " + handle.b200kv_last_cuda_error().decode()
+    if code in (1, 2, 3, 6):
+        raise ValueError(f"b200kv error {code}: {msg}")
+    raise B200KVError(code, msg)
+
+
+def strerror(code: int) -> str:
+    return lib().b200kv_strerror(int(code)).decode()

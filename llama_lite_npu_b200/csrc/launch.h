@@ -1,0 +1,72 @@
+// Internal host-side declarations shared by the .cu files and the C-ABI shim.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace b200kv {
+
+// SM count of the current device (cached per device); <= 0 on failure.
+int device_sm_count();
+// cudaGetLastError() -> B200KV_OK / B200KV_ECUDA, remembering the message.
+int check_launch();
+int record_cuda_error(cudaError_t e);
+
+int kv_append(const void* kv_values, int64_t n_tokens, int64_t src_tok_stride, const int32_t* slots,
+              void* pool, int64_t pool_tokens, int64_t pool_tok_stride, int n_rows, int head_dim,
+              int32_t* status, cudaStream_t stream);
+int kv_append_split(const void* k_values, const void* v_values, int64_t n_tokens,
+                    int64_t k_tok_stride, int64_t v_tok_stride, const int32_t* slots, void* pool,
+                    int64_t pool_tokens, int64_t pool_tok_stride, int kv_heads, int head_dim,
+                    int32_t* status, cudaStream_t stream);
+
+struct DecodeArgs {
+  const void* q;
+  int64_t q_stride_b, q_stride_h;
+  const void* k_base;
+  const void* v_base;
+  int64_t kv_tok_stride, kv_head_stride, pool_tokens;
+  const int32_t* table;
+  int64_t table_row_stride;
+  int table_kind;
+  const int32_t* row_ids;
+  const void* seq_lens;
+  int seq_lens_i64;
+  int batch, q_heads, kv_heads, head_dim, page_size;
+  float scale;
+  int64_t max_seq_len;
+  void* workspace;
+  size_t workspace_bytes;
+  void* out;
+  int64_t out_stride_b, out_stride_h;
+  int32_t* status;
+};
+size_t decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim);
+int paged_decode(const DecodeArgs& a, cudaStream_t stream);
+
+struct PrefillArgs {
+  const void* q;
+  int64_t q_stride_t, q_stride_h;
+  const void* k_base;
+  const void* v_base;
+  int64_t kv_tok_stride, kv_head_stride, pool_tokens;
+  const int32_t* table;
+  int64_t table_row_stride;
+  int table_kind;
+  const int32_t* req_ids;
+  const int32_t* q_start;
+  const void* ctx_lens;
+  const void* q_lens;
+  int lens_i64;
+  int batch;
+  int64_t total_q, max_q_len;
+  int q_heads, kv_heads, head_dim, page_size;
+  float scale_log2;
+  void* out;
+  int64_t out_stride_t, out_stride_h;
+  int32_t* status;
+};
+int paged_prefill(const PrefillArgs& a, cudaStream_t stream);
+
+}  // namespace b200kv

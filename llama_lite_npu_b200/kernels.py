@@ -1,0 +1,362 @@
+"""Operator surface of the paged-KV path, same names and positional arguments as
+the reference's ``lite_llama.kernels`` (re-exported there by ``kernels/__init__.py:4-16``
+and called from ``Attention.context_forward`` / ``token_forward``,
+``lite_llama/models/qwen3.py:20-75``).
+
+Every function validates its tensors on the host, then makes exactly one call
+into ``libb200kv.so`` through ctypes with raw device pointers and the current
+CUDA stream.  PyTorch is used for memory (outputs, the split-KV workspace) and
+streams only.  There is no CPU path: tensors must live on a CUDA device and the
+shared library must be present.
+
+Debugging aid: with the environment variable ``B200KV_DEBUG=1`` every call is
+followed by a device synchronisation and a check of the device status word
+(out-of-range slots / page ids / lengths), raising ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import _lib
+
+TABLE_BLOCK = 0
+TABLE_TOKEN = 1
+TABLE_DENSE = 2
+
+_TABLE_KINDS = {"block": TABLE_BLOCK, "token": TABLE_TOKEN, "dense": TABLE_DENSE}
+
+_DEBUG = os.environ.get("B200KV_DEBUG", "0") not in ("", "0")
+
+_status: dict[int, torch.Tensor] = {}
+_workspace: dict[int, torch.Tensor] = {}
+
+
+def _device_index(t: torch.Tensor) -> int:
+    if t.device.type != "cuda":
+        raise ValueError(
+            f"b200kv operators run on CUDA devices only (got a tensor on {t.device}); "
+            "there is no CPU fallback"
+        )
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def status_tensor(device_index: int) -> torch.Tensor:
+    """The per-device int32 status word kernels record index errors in."""
+    st = _status.get(device_index)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=f"cuda:{device_index}")
+        _status[device_index] = st
+    return st
+
+
+def check_status(device_index: Optional[int] = None) -> None:
+    """Synchronise and raise if a kernel recorded a device-side index error."""
+    if device_index is None:
+        device_index = torch.cuda.current_device()
+    st = status_tensor(device_index)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise RuntimeError(f"b200kv device status {code}: {_lib.strerror(code)}")
+
+
+def _after_call(device_index: int) -> None:
+    if _DEBUG:
+        check_status(device_index)
+
+
+def _stream(device_index: int) -> int:
+    return torch.cuda.current_stream(device_index).cuda_stream
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise ValueError(msg)
+
+
+def _lens_arg(t: torch.Tensor, name: str) -> tuple[int, int]:
+    _require(t.dtype in (torch.int32, torch.int64), f"{name} must be int32 or int64")
+    _require(t.dim() == 1 and t.is_contiguous(), f"{name} must be a contiguous 1-D tensor")
+    return t.data_ptr(), int(t.dtype == torch.int64)
+
+
+def _kv_views(k_cache: torch.Tensor, v_cache: torch.Tensor):
+    _require(k_cache.dtype == torch.float16 and v_cache.dtype == torch.float16,
+             "k_cache / v_cache must be float16")
+    _require(k_cache.dim() == 3 and v_cache.shape == k_cache.shape,
+             "k_cache / v_cache must be [tokens, kv_heads, head_dim] with equal shapes")
+    _require(k_cache.stride() == v_cache.stride() and k_cache.stride(2) == 1,
+             "k_cache / v_cache must share strides and be contiguous along head_dim")
+    return k_cache.stride(0), k_cache.stride(1), k_cache.shape[0]
+
+
+def decode_workspace(device_index: int, batch: int, q_heads: int, kv_heads: int, head_dim: int):
+    """Per-device scratch for split-KV partials; grown on demand, never shrunk, so its
+    address is stable across calls of the same or a smaller shape."""
+    with torch.cuda.device(device_index):
+        need = _lib.lib().b200kv_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim)
+    if need == 0:
+        raise ValueError(
+            "unsupported decode shape: head_dim must be 128 and q_heads/kv_heads an integer <= 16"
+        )
+    ws = _workspace.get(device_index)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{device_index}")
+        _workspace[device_index] = ws
+    return ws
+
+
+@torch.no_grad()
+def update_kv_buffer(KV_Values: torch.Tensor, Select_Index: torch.Tensor, KV_Buffer: torch.Tensor) -> None:
+    """``KV_Buffer[Select_Index[i], :, :] = KV_Values[i, :, :]`` in place, bit-exact.
+
+    Same contract as the reference's ``update_kv_buffer``
+    (``lite_llama/kernels/update_kv_buffer.py:47-81``): ``KV_Values`` is
+    ``[num_tokens, 2*kv_heads, head_dim]`` fp16, ``Select_Index`` the int32
+    slot_mapping, ``KV_Buffer`` the ``[pool_tokens, 2*kv_heads, head_dim]`` page pool.
+    """
+    dev = _device_index(KV_Buffer)
+    _require(KV_Values.device == KV_Buffer.device and Select_Index.device == KV_Buffer.device,
+             "KV_Values, Select_Index and KV_Buffer must be on the same device")
+    _require(KV_Values.dtype == torch.float16 and KV_Buffer.dtype == torch.float16,
+             "KV_Values and KV_Buffer must be float16")
+    _require(Select_Index.dtype == torch.int32 and Select_Index.dim() == 1,
+             "Select_Index must be a 1-D int32 tensor")
+    _require(KV_Values.dim() == 3 and KV_Buffer.dim() == 3, "KV_Values and KV_Buffer must be 3-D")
+    assert KV_Values.shape[1] == KV_Buffer.shape[1] and KV_Values.shape[2] == KV_Buffer.shape[2]
+    n = Select_Index.shape[0]
+    _require(KV_Values.shape[0] >= n, "KV_Values has fewer rows than Select_Index")
+    if n == 0:
+        return
+    rows, d = KV_Values.shape[1], KV_Values.shape[2]
+    _require(KV_Values.stride(2) == 1 and KV_Values.stride(1) == d,
+             "KV_Values must be contiguous inside a token")
+    _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d,
+             "KV_Buffer must be contiguous inside a token")
+    if not Select_Index.is_contiguous():
+        Select_Index = Select_Index.contiguous()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().b200kv_kv_append(
+            KV_Values.data_ptr(), n, KV_Values.stride(0), Select_Index.data_ptr(),
+            KV_Buffer.data_ptr(), KV_Buffer.shape[0], KV_Buffer.stride(0), rows, d,
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+
+
+@torch.no_grad()
+def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: torch.Tensor,
+                           KV_Buffer: torch.Tensor) -> None:
+    """Same scatter from separate ``xk`` / ``xv`` ``[num_tokens, kv_heads, head_dim]`` tensors,
+    i.e. ``update_kv_buffer(torch.cat([xk, xv], dim=-2), ...)`` without the concatenation
+    (the reference concatenates first, ``lite_llama/models/qwen3.py:29,62``)."""
+    dev = _device_index(KV_Buffer)
+    _require(xk.dtype == torch.float16 and xv.dtype == torch.float16
+             and KV_Buffer.dtype == torch.float16, "xk, xv and KV_Buffer must be float16")
+    _require(xk.dim() == 3 and xk.shape == xv.shape, "xk and xv must be 3-D with equal shapes")
+    _require(Select_Index.dtype == torch.int32 and Select_Index.dim() == 1,
+             "Select_Index must be a 1-D int32 tensor")
+    kvh, d = xk.shape[1], xk.shape[2]
+    _require(KV_Buffer.dim() == 3 and KV_Buffer.shape[1] == 2 * kvh and KV_Buffer.shape[2] == d,
+             "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim]")
+    for t, name in ((xk, "xk"), (xv, "xv"), (KV_Buffer, "KV_Buffer")):
+        _require(t.stride(2) == 1 and t.stride(1) == d, f"{name} must be contiguous inside a token")
+    n = Select_Index.shape[0]
+    _require(xk.shape[0] >= n, "xk has fewer rows than Select_Index")
+    if n == 0:
+        return
+    if not Select_Index.is_contiguous():
+        Select_Index = Select_Index.contiguous()
+    with torch.cuda.device(dev):
+        rc = _lib.lib().b200kv_kv_append_split(
+            xk.data_ptr(), xv.data_ptr(), n, xk.stride(0), xv.stride(0), Select_Index.data_ptr(),
+            KV_Buffer.data_ptr(), KV_Buffer.shape[0], KV_Buffer.stride(0), kvh, d,
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+
+
+@torch.no_grad()
+def flash_decoding(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    qk_scale: float,
+    b_req_tokens_table: torch.Tensor,
+    b_seq_len: torch.Tensor,
+    max_actual_seq_len: int,
+    *,
+    b_req_idx: Optional[torch.Tensor] = None,
+    table_kind: str = "token",
+    page_size: int = 16,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Paged decode attention; returns a new ``[batch, q_heads, head_dim]`` fp16 tensor.
+
+    Positional arguments are those of the reference's ``flash_decoding``
+    (``lite_llama/kernels/flashdecoding.py:295-342``): ``k_cache`` / ``v_cache`` are the
+    strided K and V views of one layer's pool, ``qk_scale`` the natural softmax scale,
+    ``b_req_tokens_table`` the logical-token -> physical-slot table whose row ``i`` belongs to
+    batch position ``i`` (the reference indexes rows by batch position, ``:48,85``),
+    ``b_seq_len`` int32/int64 lengths, ``max_actual_seq_len`` a host upper bound on them.
+
+    Keyword extensions: ``b_req_idx`` (int32 ``[batch]``) selects table rows explicitly, which
+    a continuous batch with gaps needs; ``table_kind="block"`` passes a page-id table
+    ``[rows, max_pages]`` instead of a token table.
+    """
+    dev = _device_index(q)
+    _require(q.dtype == torch.float16 and q.dim() == 3, "q must be float16 [batch, heads, head_dim]")
+    assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
+    _require(q.stride(2) == 1, "q must be contiguous along head_dim")
+    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
+    batch, q_heads, d = q.shape
+    kv_heads = k_cache.shape[1]
+    kind = _TABLE_KINDS[table_kind]
+    _require(kind in (TABLE_BLOCK, TABLE_TOKEN), "decode takes a 'token' or 'block' table")
+    tbl = b_req_tokens_table
+    _require(tbl.dtype == torch.int32 and tbl.dim() == 2 and tbl.stride(1) == 1,
+             "the table must be a 2-D int32 tensor contiguous along its last dimension")
+    _require(b_seq_len.shape[0] == batch, "b_seq_len must have one entry per batch row")
+    lens_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
+    rows_ptr = 0
+    if b_req_idx is not None:
+        _require(b_req_idx.dtype == torch.int32 and b_req_idx.shape == (batch,)
+                 and b_req_idx.is_contiguous(), "b_req_idx must be contiguous int32 [batch]")
+        rows_ptr = b_req_idx.data_ptr()
+    else:
+        _require(tbl.shape[0] >= batch, "the table has fewer rows than the batch")
+    width_tokens = tbl.shape[1] * (page_size if kind == TABLE_BLOCK else 1)
+    max_len = int(max_actual_seq_len)
+    _require(0 <= max_len <= width_tokens, "max_actual_seq_len exceeds the table width")
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _require(out.shape == q.shape and out.dtype == torch.float16 and out.stride(2) == 1,
+                 "out must match q")
+    if batch == 0:
+        return out
+    ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().b200kv_paged_decode(
+            q.data_ptr(), q.stride(0), q.stride(1),
+            k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
+            tbl.data_ptr(), tbl.stride(0), kind, rows_ptr, lens_ptr, lens_i64,
+            batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
+            ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+    return out
+
+
+def _prefill_call(q, k_cache, v_cache, scale_log2, tbl_ptr, tbl_stride, kind, req_ids_ptr,
+                  q_start_loc, ctx_ptr, qlen_ptr, lens_i64, batch, max_q_len, page_size):
+    dev = _device_index(q)
+    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
+    total_q, q_heads, d = q.shape
+    kv_heads = k_cache.shape[1]
+    output = torch.empty_like(q)
+    if q.numel() == 0 or batch == 0:
+        return output
+    with torch.cuda.device(dev):
+        rc = _lib.lib().b200kv_paged_prefill(
+            q.data_ptr(), q.stride(0), q.stride(1),
+            k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
+            tbl_ptr, tbl_stride, kind, req_ids_ptr, q_start_loc.data_ptr(),
+            ctx_ptr, qlen_ptr, lens_i64, batch, total_q, int(max_q_len),
+            q_heads, kv_heads, d, int(page_size), float(scale_log2),
+            output.data_ptr(), output.stride(0), output.stride(1),
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+    return output
+
+
+@torch.no_grad()
+def paged_chunk_flash_attention(
+    q: torch.Tensor,
+    k_cache: torch.Tensor,
+    v_cache: torch.Tensor,
+    sm_scale: float,
+    req_token_table: torch.Tensor,
+    req_ids: torch.Tensor,
+    q_start_loc: torch.Tensor,
+    context_lens: torch.Tensor,
+    q_seq_lens: torch.Tensor,
+    max_q_len: int,
+    *,
+    table_kind: str = "token",
+    page_size: int = 16,
+) -> torch.Tensor:
+    """Causal attention of a packed query chunk over historical paged KV plus the chunk's own
+    KV (already appended to the pool).  Same positional arguments as the reference's
+    ``paged_chunk_flash_attention`` (``lite_llama/kernels/paged_chunk_flashattention.py:227-327``);
+    ``sm_scale`` is the softmax scale already multiplied by log2(e), as the reference's callers
+    pass it (``lite_llama/models/qwen3.py:296``).  Returns a tensor like ``q``."""
+    _device_index(q)
+    _require(q.dtype == torch.float16 and q.dim() == 3 and q.stride(2) == 1,
+             "q must be float16 [tokens, heads, head_dim], contiguous along head_dim")
+    kind = _TABLE_KINDS[table_kind]
+    _require(kind in (TABLE_BLOCK, TABLE_TOKEN), "paged prefill takes a 'token' or 'block' table")
+    tbl = req_token_table
+    _require(tbl.dtype == torch.int32 and tbl.dim() == 2 and tbl.stride(1) == 1,
+             "the table must be a 2-D int32 tensor contiguous along its last dimension")
+    batch = int(q_seq_lens.shape[0])
+    _require(req_ids.dtype == torch.int32 and req_ids.shape == (batch,) and req_ids.is_contiguous(),
+             "req_ids must be contiguous int32 [batch]")
+    _require(q_start_loc.dtype == torch.int32 and q_start_loc.shape == (batch,)
+             and q_start_loc.is_contiguous(), "q_start_loc must be contiguous int32 [batch]")
+    _require(context_lens.dtype == q_seq_lens.dtype and context_lens.shape == (batch,),
+             "context_lens and q_seq_lens must share dtype and shape")
+    ctx_ptr, lens_i64 = _lens_arg(context_lens, "context_lens")
+    qlen_ptr, _ = _lens_arg(q_seq_lens, "q_seq_lens")
+    return _prefill_call(q, k_cache, v_cache, sm_scale, tbl.data_ptr(), tbl.stride(0), kind,
+                         req_ids.data_ptr(), q_start_loc, ctx_ptr, qlen_ptr, lens_i64, batch,
+                         max_q_len, page_size)
+
+
+@torch.no_grad()
+def flash_attention2_no_pad(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    sm_scale: float,
+    b_start_loc: torch.Tensor,
+    b_seq_len: torch.Tensor,
+    max_seq_len: int,
+) -> torch.Tensor:
+    """Causal attention inside each packed segment ``[start, start+len)`` of dense ``q``/``k``/``v``
+    (``[tokens, heads, head_dim]`` fp16, K/V with the KV head count).  Same positional
+    arguments as the reference's ``flash_attention2_no_pad``
+    (``lite_llama/kernels/flashattention2_nopad.py:171-221``); ``sm_scale`` already carries
+    log2(e).  Runs the paged prefill kernel with zero history and the packed K/V as the pool."""
+    _device_index(q)
+    _require(q.dtype == torch.float16 and q.dim() == 3 and q.stride(2) == 1,
+             "q must be float16 [tokens, heads, head_dim], contiguous along head_dim")
+    batch = int(b_seq_len.shape[0])
+    _require(b_start_loc.dtype == torch.int32 and b_start_loc.shape == (batch,)
+             and b_start_loc.is_contiguous(), "b_start_loc must be contiguous int32 [batch]")
+    qlen_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
+    zeros = torch.zeros_like(b_seq_len)
+    return _prefill_call(q, k, v, sm_scale, 0, 0, TABLE_DENSE, 0, b_start_loc,
+                         zeros.data_ptr(), qlen_ptr, lens_i64, batch, max_seq_len, 16)
+
+
+__all__ = [
+    "update_kv_buffer",
+    "update_kv_buffer_split",
+    "flash_decoding",
+    "paged_chunk_flash_attention",
+    "flash_attention2_no_pad",
+    "check_status",
+    "status_tensor",
+    "decode_workspace",
+]

@@ -1,0 +1,200 @@
+"""Seeded input builders shared by the golden-vector generator and the tests.
+
+Every builder is a pure function of its case name, built on the bit-reproducible hash
+generator of ``llama_lite_npu_b200.workloads``, so the generator script (which runs the
+reference) and the tests (which run the oracle and the CUDA kernels) see identical inputs.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from llama_lite_npu_b200 import workloads as W
+
+# name -> (DecodeConfig, explicit lengths or None)
+DECODE_CASES = {
+    "decode_gqa4_edges": (W.DecodeConfig("decode_gqa4_edges", 6, 8, 2, 64, 1, 1, seed=11),
+                          [1, 15, 16, 17, 64, 203]),
+    "decode_gqa8_small": (W.DecodeConfig("decode_gqa8_small", 5, 16, 2, 96, 1, 1, seed=12),
+                          [300, 129, 128, 33, 250]),
+    "decode_c1_shape": (W.DecodeConfig("decode_c1_shape", 4, 16, 8, 512, 64, 512, seed=1001), None),
+    "decode_mha": (W.DecodeConfig("decode_mha", 3, 2, 2, 32, 1, 1, seed=13), [7, 100, 48]),
+}
+
+# name -> (PrefillConfig, prompt lengths, shared pages)
+PREFILL_CASES = {
+    "prefill_hist_gqa2": (W.PrefillConfig("prefill_hist_gqa2", 3, 4, 2, 48, 1, 1, seed=21),
+                          [40, 130, 77], [1, 3, 0]),
+    "prefill_hist_gqa8_edges": (W.PrefillConfig("prefill_hist_gqa8_edges", 4, 8, 1, 64, 1, 1, seed=22),
+                                [17, 129, 128, 1], [1, 4, 7, 0]),
+}
+
+# name -> (heads, [segment lengths])
+NOPAD_CASES = {
+    "nopad_mha": (2, [33, 100, 1, 64]),
+}
+
+# name -> (tokens, rows, pool_tokens)
+APPEND_CASES = {
+    "append_decode": (4, 16, 8192),
+    "append_prefill": (333, 4, 1024),
+}
+
+MHA_DECODE_CASES = {
+    "decode_contiguous_mha": (3, 4, [50, 128, 77]),
+}
+
+
+def build_decode(name: str, device="cpu") -> W.DecodeCase:
+    cfg, lens = DECODE_CASES[name]
+    return W.make_decode_case(cfg, device=device, fill="hash",
+                              lengths=None if lens is None else np.array(lens))
+
+
+def build_prefill(name: str, device="cpu") -> W.PrefillCase:
+    cfg, prompts, shared = PREFILL_CASES[name]
+    return W.make_prefill_case(cfg, device=device, fill="hash", prompt_lens=np.array(prompts),
+                               shared_pages=np.array(shared))
+
+
+def build_nopad(name: str, device="cpu"):
+    heads, lens = NOPAD_CASES[name]
+    total = int(sum(lens))
+    seed = 31
+    q = W.hash_normal_fp16(seed, (total, heads, 128), 1).to(device)
+    k = W.hash_normal_fp16(seed, (total, heads, 128), 2).to(device)
+    v = W.hash_normal_fp16(seed, (total, heads, 128), 3).to(device)
+    start = torch.tensor(np.concatenate([[0], np.cumsum(lens)[:-1]]), dtype=torch.int32, device=device)
+    return q, k, v, start, torch.tensor(lens, dtype=torch.int32, device=device)
+
+
+def build_append(name: str, device="cpu"):
+    n, rows, pool_tokens = APPEND_CASES[name]
+    seed = 41 + n
+    src = W.hash_normal_fp16(seed, (n, rows, 128), 1).to(device)
+    pool = W.hash_normal_fp16(seed, (pool_tokens, rows, 128), 2).to(device)
+    slots = torch.from_numpy(W.hash_permutation(seed, pool_tokens, 3)[:n].astype(np.int32)).to(device)
+    return src, slots, pool
+
+
+def build_mha_decode(name: str, device="cpu"):
+    batch, heads, lens = MHA_DECODE_CASES[name]
+    seed = 51
+    total = int(sum(lens))
+    q = W.hash_normal_fp16(seed, (batch, heads, 128), 1).to(device)
+    k = W.hash_normal_fp16(seed, (total, heads, 128), 2).to(device)
+    v = W.hash_normal_fp16(seed, (total, heads, 128), 3).to(device)
+    start = torch.tensor(np.concatenate([[0], np.cumsum(lens)[:-1]]), dtype=torch.int32, device=device)
+    return q, k, v, start, torch.tensor(lens, dtype=torch.int32, device=device)
+
+
+def host_script(paged, kveng) -> dict:
+    """Drive the page-pool classes of module ``paged`` and the metadata classes of module
+    ``kveng`` through a fixed script and return everything observable as plain data."""
+    log: dict = {}
+    pm = paged.PagedKVCacheManager(num_layers=1, num_kv_heads=1, head_dim=8, num_pages=12,
+                                   page_size=4, dtype=torch.float16, device="cpu")
+    rm = paged.PagedReqTokensManager(max_requests=4, max_seq_len=24, page_manager=pm, device="cpu")
+
+    def snap(tag):
+        log[tag] = {
+            "free": int(pm.num_free_pages),
+            "page_free": pm.page_free.int().tolist(),
+            "refcount": pm.page_refcount.tolist(),
+            "req_pages": {str(k): [int(x) for x in v.tolist()] for k, v in sorted(rm.req_page_table.items())},
+            "req_tokens": {str(k): int(v) for k, v in sorted(rm.req_token_count.items())},
+            "free_reqs": list(rm.free_req_indices),
+            "tables": {str(k): rm.b_req_tokens_table[k, : rm.req_token_count[k]].tolist()
+                       for k in sorted(rm.req_token_count)},
+        }
+
+    r0 = rm.reserve_req(5)
+    r1 = rm.reserve_req(num_tokens=1, reserved_tokens=9)
+    log["ids_a"] = [r0, r1]
+    snap("after_reserve")
+    log["extend_r1_8"] = rm.extend_req(r1, 8)
+    log["extend_r0_3"] = rm.extend_req(r0, 3)
+    log["extend_r0_1"] = rm.extend_req(r0, 1)
+    snap("after_extend")
+    r2 = rm.reserve_shared_req(rm.req_page_table[r0], 8)
+    log["ids_b"] = [r2]
+    snap("after_share")
+    ids, lens, last = rm.batch_metadata([r2, r0, r1])
+    log["batch_metadata"] = [ids.tolist(), lens.tolist(), last.tolist(),
+                             str(ids.dtype), str(lens.dtype), str(last.dtype)]
+    log["ensure_r1_16"] = rm.ensure_req_capacity(r1, 16)
+    log["ensure_r1_99"] = rm.ensure_req_capacity(r1, 99)
+    snap("after_ensure")
+    rm.free_req(r0)
+    snap("after_free_r0")
+    log["too_long"] = rm.reserve_req(25)
+    r3 = rm.reserve_req(17)
+    log["ids_c"] = [r3]
+    log["exhaust"] = rm.reserve_req(16)
+    log["extend_over_max"] = rm.extend_req(r3, 8)
+    snap("after_r3")
+    log["request_pages_r2"] = list(rm.request_pages(r2))
+    rm.free_req(r2)
+    rm.free_req(r1)
+    rm.free_req(r3)
+    snap("after_free_all")
+    errs = {}
+    try:
+        pm.free(torch.tensor([0]))
+    except ValueError as e:
+        errs["free_free_page"] = str(e)
+    try:
+        pm.add_ref(torch.tensor([1]))
+    except ValueError as e:
+        errs["addref_free_page"] = str(e)
+    try:
+        rm.batch_metadata([])
+    except ValueError as e:
+        errs["empty_batch"] = str(e)
+    try:
+        rm.batch_metadata([3])
+    except KeyError as e:
+        errs["unknown_req"] = str(e)
+    try:
+        rm.request_pages(2)
+    except KeyError as e:
+        errs["unknown_pages"] = str(e)
+    log["errors"] = errs
+
+    refs = kveng.KVBlockRefCounter(total_blocks=6)
+    a = refs.acquire(3)
+    refs.add_ref((0, 2))
+    refs.release((0, 1))
+    b = refs.acquire(2)
+    k = {"a": list(a), "b": list(b), "avail": refs.available_count,
+         "rc": [refs.refcount(i) for i in range(6)]}
+    for label, fn, exc in (
+        ("neg", lambda: refs.release((5,)), ValueError),
+        ("free_ref", lambda: refs.add_ref((5,)), ValueError),
+        ("range", lambda: refs.refcount(6), IndexError),
+        ("short", lambda: refs.acquire(9), RuntimeError),
+        ("zero", lambda: refs.acquire(0), ValueError),
+    ):
+        try:
+            fn()
+            k[label] = "no error"
+        except exc as e:
+            k[label] = type(e).__name__
+    log["refcounter"] = k
+
+    cache = kveng.PrefixCache(block_size=4)
+    cache.put((1, 2, 3, 4, 5, 6, 7, 8, 9), (10, 11, 12))
+    m1 = cache.match((1, 2, 3, 4, 5, 6, 9, 9))
+    m2 = cache.match((1, 2, 3, 4, 5, 6, 7, 8, 9, 9, 9, 9))
+    m3 = cache.match((5, 6, 7, 8))
+    m4 = cache.match((1, 2, 3))
+    log["prefix"] = [[m.matched_tokens, list(m.block_ids)] for m in (m1, m2, m3, m4)]
+    plan = kveng.ChunkedPrefillPlanner(chunk_size=4).plan(10)
+    log["chunks"] = [[c.start, c.end, c.length] for c in plan]
+    log["chunks_empty"] = len(kveng.ChunkedPrefillPlanner(chunk_size=3).plan(0))
+    pk = kveng.MixedLengthPrefillPacker().pack(((10, 11), (20,), (), (30, 31, 32)))
+    log["pack"] = {"tokens": list(pk.flat_token_ids), "pos": list(pk.flat_position_ids),
+                   "rows": [[r.request_index, r.start, r.length, r.end] for r in pk.requests],
+                   "total": pk.total_tokens, "batch": pk.batch_size}
+    return log
