@@ -24,6 +24,7 @@ SOURCES = (
     "b200kv_capi.cu",
     "kv_append.cu",
     "paged_decode.cu",
+    "tma.cu",
     "paged_prefill_sm100.cu",
 )
 

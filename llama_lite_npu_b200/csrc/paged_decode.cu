@@ -21,14 +21,16 @@
 //
 // Pipeline inside a CTA (128 threads, 4 warps, 2 CTAs per SM): tiles of 64 tokens (4
 // pages; K and V rows of 256 B each) are staged through a 3-deep cp.async ring of 32 KB
-// stages that keeps running across piece boundaries; shared-memory rows are XOR-swizzled
+// stages that keeps running across piece boundaries (the page-table entries of a tile are
+// fetched three tiles before its copies are issued); shared-memory rows are XOR-swizzled
 // in 16-byte chunks so ldmatrix is conflict-free.  Warp w owns tokens [16w, 16w+16) of
-// every tile: S = Q K^T and O += P V run on mma.sync m16n8k16 (fp16 in, fp32 accumulate)
-// with the G query heads as the M rows; per-warp online-softmax states are merged through
-// shared memory at the end of a piece.  The kernel is HBM-bound: algorithmic bytes per
-// token per KV head = 2 (K,V) * 128 * 2 B.
+// every tile: S^T = K Q^T and O^T += V^T P^T run on mma.sync m16n8k16 (fp16 in, fp32
+// accumulate) with the tokens as the M rows and the G query heads as the N columns;
+// per-warp online-softmax states are merged through shared memory at the end of a piece.
+// The kernel is HBM-bound: algorithmic bytes per token per KV head = 2 (K,V) * 128 * 2 B.
 #include "common.cuh"
 #include "launch.h"
+#include "tma.h"
 
 namespace b200kv {
 
@@ -38,14 +40,24 @@ constexpr int kD = 128;
 constexpr int kPS = 16;
 constexpr int kTileTok = 64;
 constexpr int kTilePages = kTileTok / kPS;
-constexpr int kWarps = 4;
-constexpr int kThreads = kWarps * 32;
+constexpr int kConsumerWarps = 4;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
+constexpr int kScanThreads = 128;
 constexpr int kRowBytes = kD * 2;
+constexpr int kPageBytes = kPS * kRowBytes;       // one page of one head, K or V: 4 KB
 constexpr int kTileBytes = kTileTok * kRowBytes;  // one of K or V
 constexpr int kStageBytes = 2 * kTileBytes;
-constexpr int kCtasPerSm = 2;
+// Tunables; the -D overrides exist for tuning sweeps, the defaults are what ships.
+#ifndef B200KV_DECODE_CTAS_PER_SM
+#define B200KV_DECODE_CTAS_PER_SM 2
+#endif
+#ifndef B200KV_DECODE_STAGES
+#define B200KV_DECODE_STAGES 3
+#endif
+constexpr int kCtasPerSm = B200KV_DECODE_CTAS_PER_SM;
+constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
 constexpr int kMinPagesPerTeam = 8;
-constexpr int kCombineThreads = 256;
+constexpr int kCombineThreads = 128;
 
 struct DecodeParams {
   const __half* q;
@@ -151,74 +163,111 @@ struct Walker {
   }
 };
 
-// Token slot of the first row of each page of a tile, or -1 (zero-fill) when the tile has no
-// such page or the table entry is out of range.
-__device__ __forceinline__ void load_page_bases(const DecodeParams& p, const Tile& t, bool valid,
-                                                int64_t (&base)[kTilePages]) {
+// What the producer needs to issue one tile.  The table entries are kept RAW (undecoded and
+// unchecked) so that nothing depends on the loaded values until the tile is issued, kLead
+// tiles after the loads were started: the table latency is off the producer's critical path.
+constexpr int kLead = 4;
+struct Fetch {
+  int ntok;    // valid tokens of the tile; 0 = no tile
+  int npages;  // pages of the tile
+  int32_t id[kTilePages];
+};
+
+__device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fetch& f) {
+  Tile t;
+  f.ntok = 0;
+  f.npages = 0;
+#pragma unroll
+  for (int i = 0; i < kTilePages; ++i) f.id[i] = 0;
+  if (!w.next(p, t)) return;
+  f.ntok = t.ntok;
+  f.npages = t.npages;
+  const int32_t* rowp = p.table + static_cast<int64_t>(t.row) * p.table_row_stride;
 #pragma unroll
   for (int i = 0; i < kTilePages; ++i) {
-    base[i] = -1;
-    if (valid && i < t.npages) {
-      const int lp = t.page0 + i;
-      const int32_t* rowp = p.table + static_cast<int64_t>(t.row) * p.table_row_stride;
-      int64_t s = (p.table_kind == B200KV_TABLE_BLOCK)
-                      ? static_cast<int64_t>(__ldg(rowp + lp)) * kPS
-                      : static_cast<int64_t>(__ldg(rowp + static_cast<int64_t>(lp) * kPS));
-      if (s < 0 || s + kPS > p.pool_tokens) {
-        set_status(p.status, B200KV_DEV_BAD_PAGE);
-        s = -1;
-      }
-      base[i] = s;
+    if (i < t.npages) {
+      const int64_t lp = t.page0 + i;
+      f.id[i] = __ldg(rowp + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
     }
   }
 }
 
-// Issue the cp.async copies of one tile (K then V) for KV head `head` into a stage.
-__device__ __forceinline__ void issue_tile(const DecodeParams& p, int head, int ntok,
-                                           const int64_t (&base)[kTilePages], uint32_t stage_smem,
-                                           uint64_t policy) {
-  const int tid = threadIdx.x;
-  const int c = tid & 15;        // 16-byte chunk inside the 256-byte row
-  const int r0 = tid >> 4;       // rows r0, r0+8, ..., r0+56
-  const __half* kh = p.k_base + static_cast<int64_t>(head) * p.kv_head_stride + c * 8;
-  const __half* vh = p.v_base + static_cast<int64_t>(head) * p.kv_head_stride + c * 8;
-#pragma unroll
-  for (int j = 0; j < kTileTok / 8; ++j) {
-    const int r = r0 + 8 * j;
-    const int64_t pb = base[j >> 1];  // page of row r is r / 16 == j / 2
-    const bool ok = (r < ntok) && (pb >= 0);
-    const int64_t off = ok ? (pb + (r & (kPS - 1))) * p.kv_tok_stride : 0;
-    const uint32_t dst = stage_smem + r * kRowBytes + ((c ^ (r & 7)) << 4);
-    cp_async_16_hint(dst, kh + off, ok ? 16 : 0, policy);
-    cp_async_16_hint(dst + kTileBytes, vh + off, ok ? 16 : 0, policy);
-  }
+// Transpose an 8x8 matrix of b16 held in mma-fragment layout (lane l: row l/4, cols 2(l%4)..+1).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(d) : "r"(a));
+  return d;
 }
 
+// Shared-memory image of one page of one head as the two TMA boxes leave it: two blocks of
+// 16 rows x 128 B (head_dim halves [0,64) and [64,128)), each row's 16-byte chunks XOR-swizzled
+// with row % 8.  Byte offset of chunk c (0..15 across the 256-byte head row) of token row r.
+__device__ __forceinline__ uint32_t page_chunk_off(int r, int c) {
+  return static_cast<uint32_t>(((c >> 3) << 11) + (r << 7) + (((c & 7) ^ (r & 7)) << 4));
+}
+
+// Kernel structure: warp 4 is the producer (walks the page line, waits for a free stage, arms
+// its "full" mbarrier with the byte count and issues the tile's 16 TMA copies from 16 lanes);
+// warps 0..3 are consumers (wait "full", compute their page of the tile, arrive on "empty").
+//
+// MMA roles: the 16 tokens a consumer warp owns (exactly one page) are the M rows, the (padded)
+// query heads of the group the N columns.  S^T[tok, head] = K[tok, d] . Q^T[d, head] takes K as
+// the A operand straight from shared memory; P^T is transposed in registers (movmatrix) into the
+// B operand of O^T[d, head] += V^T[d, tok] . P^T[tok, head], whose A operand is V read with
+// ldmatrix.trans.  With N = 8 a group of up to 8 query heads wastes no tensor work; ROWS = 16
+// uses two N blocks.
 template <int ROWS, int STAGES>
-__global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kernel(DecodeParams p) {
-  static_assert(ROWS == 8 || ROWS == 16, "query-group rows are padded to 8 or 16");
-  extern __shared__ __align__(128) uint8_t smem[];
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
+paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
+                          const __grid_constant__ CUtensorMap vmap) {
+  static_assert(ROWS == 8 || ROWS == 16, "query-group heads are padded to 8 or 16");
+  constexpr int NB = ROWS / 8;
+  extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stages = smem;
-  float* merge_o = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [4][ROWS][128]
-  float* merge_ml = merge_o + kWarps * ROWS * kD;                          // [4][ROWS][2]
-  int* scan = reinterpret_cast<int*>(merge_o);  // start-up only: [kThreads + 1] page prefix
+  float* merge_o = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [4][128][ROWS]
+  float* merge_ml = merge_o + kConsumerWarps * kD * ROWS;                  // [4][ROWS][2]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(merge_ml + kConsumerWarps * ROWS * 2);
+  int* scan = reinterpret_cast<int*>(merge_o);  // start-up only: [kScanThreads + 1] page prefix
 
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int team = blockIdx.x / p.kv_heads;
   const int head = blockIdx.x - team * p.kv_heads;
+  // Let the merge kernel be scheduled behind us right away; it waits for this whole grid with
+  // cudaGridDependencySynchronize() before touching any partial.
+  cudaTriggerProgrammaticLaunchCompletion();
+
+  const uint32_t stage_base = smem_u32(stages);
+  const uint32_t bar_full = smem_u32(bars);                 // [STAGES]
+  const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
+  const uint32_t bar_merge_ready = bar_empty + 8 * STAGES;  // consumers wrote their partial state
+  const uint32_t bar_merge_free = bar_merge_ready + 8;      // consumers finished reading it
+  if ((stage_base & 1023u) != 0) {  // the swizzled TMA boxes need 1024-byte aligned stages
+    set_status(p.status, B200KV_DEV_BAD_PAGE);
+    return;
+  }
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, kConsumerWarps);
+    }
+    mbar_init(bar_merge_ready, kConsumerWarps);
+    mbar_init(bar_merge_free, kConsumerWarps);
+    fence_barrier_init();
+  }
 
   // ---- where does this team's page range start? -------------------------------------------
-  // Thread t sums the pages of sequences [t*per, (t+1)*per); an exclusive scan over the 128
-  // sums gives NP and the chunk holding the range start, then a short linear walk finds it.
-  const int per = (p.batch + kThreads - 1) / kThreads;
-  {
-    int s = 0;
+  // Thread t < 128 sums the pages of sequences [t*per, (t+1)*per); an exclusive scan over the
+  // 128 sums gives NP and the chunk holding the range start, then a short linear walk finds it.
+  const int per = (p.batch + kScanThreads - 1) / kScanThreads;
+  if (tid < kScanThreads) {
+    int sum = 0;
     const int lo = tid * per;
     const int hi = min(p.batch, lo + per);
-    for (int b = lo; b < hi; ++b) s += pages_of(seq_len_checked(p, b));
-    scan[tid + 1] = s;
+    for (int b = lo; b < hi; ++b) sum += pages_of(seq_len_checked(p, b));
+    scan[tid + 1] = sum;
     if (tid == 0) scan[0] = 0;
   }
   __syncthreads();
@@ -241,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
     for (int i = 0; i < 4; ++i) scan[1 + lane * 4 + i] = v[i] + excl;
   }
   __syncthreads();
-  const int64_t np_total = scan[kThreads];
+  const int64_t np_total = scan[kScanThreads];
   const int nteams_eff = effective_teams(p.nteams, np_total);
   if (np_total == 0 || team >= nteams_eff) return;
   const int64_t r_begin = team_begin(team, nteams_eff, np_total);
@@ -250,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
   int start_b, start_page;
   {
     // last chunk whose prefix <= r_begin
-    int lo = 0, hi = kThreads - 1;
+    int lo = 0, hi = kScanThreads - 1;
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
       if (scan[mid] <= r_begin) lo = mid; else hi = mid - 1;
@@ -266,195 +315,245 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
     start_b = b;
     start_page = static_cast<int>(r_begin - acc);
   }
-  __syncthreads();  // the scan scratch aliases the merge buffer
+  __syncthreads();  // the scan scratch aliases the merge buffer; barrier inits are visible
 
-  const uint64_t policy = l2_evict_first_policy();
-  const uint32_t stage_base = smem_u32(stages);
-
-  Walker prod, cons;
-  prod.flat = cons.flat = r_begin;
-  prod.flat_end = cons.flat_end = r_end;
-  prod.enter(p, start_b, start_page);
-  cons.enter(p, start_b, start_page);
-
-  // ---- prologue: STAGES-1 tiles in flight, plus the page ids of the next one -----------------
-  Tile pend;
-  int64_t pend_base[kTilePages];
-  bool pend_valid = prod.next(p, pend);
-  load_page_bases(p, pend, pend_valid, pend_base);
+  // ================================= producer warp ==========================================
+  // All 32 lanes walk the page line in lock step (cheap, uniform); lane 0 arms the stage's
+  // "full" barrier with the byte count, then lanes 0..15 each issue ONE of the tile's copies:
+  // lane = 4*page + {K low half, K high half, V low half, V high half}.
+  if (warp == kConsumerWarps) {
+    if (lane == 0) {
+      prefetch_tensormap(&kmap);
+      prefetch_tensormap(&vmap);
+    }
+    const uint64_t policy = l2_evict_first_policy();
+    Walker prod;
+    prod.flat = r_begin;
+    prod.flat_end = r_end;
+    prod.enter(p, start_b, start_page);
+    Fetch fq[kLead];
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (pend_valid) issue_tile(p, head, pend.ntok, pend_base, stage_base + s * kStageBytes, policy);
-    cp_async_commit();
-    pend_valid = prod.next(p, pend);
-    load_page_bases(p, pend, pend_valid, pend_base);
+    for (int i = 0; i < kLead; ++i) fetch_next(p, prod, fq[i]);
+    const int my_page = lane >> 2;
+    const int my_part = lane & 3;
+    const CUtensorMap* my_map = (my_part & 2) ? &vmap : &kmap;
+    const uint32_t my_off = my_page * kPageBytes + (my_part & 1) * (kPageBytes / 2) +
+                            ((my_part & 2) ? kTileBytes : 0);
+    for (int it = 0;; ++it) {
+      const Fetch f = fq[0];
+      if (f.ntok == 0) break;
+      const int st = it % STAGES;
+      if (it >= STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((it / STAGES) - 1) & 1)) {
+        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+        break;  // consumers run into their own bounded waits and leave too
+      }
+      const uint32_t full = bar_full + 8 * st;
+      if (lane == 0)
+        mbar_arrive_expect_tx(full, static_cast<uint32_t>(f.npages) * (2 * kPageBytes));
+      __syncwarp();
+      if (lane < 4 * f.npages) {
+        int32_t id = f.id[0];
+#pragma unroll
+        for (int i = 1; i < kTilePages; ++i) id = (my_page == i) ? f.id[i] : id;
+        int64_t slot = (p.table_kind == B200KV_TABLE_BLOCK) ? static_cast<int64_t>(id) * kPS
+                                                            : static_cast<int64_t>(id);
+        if (slot < 0 || slot + kPS > p.pool_tokens) {
+          // never dereference a bad entry: report it and read page 0 instead
+          set_status(p.status, B200KV_DEV_BAD_PAGE);
+          slot = 0;
+        }
+        tma_load_3d(stage_base + st * kStageBytes + my_off, my_map, full, (my_part & 1) * 64, head,
+                    static_cast<int>(slot), policy);
+      }
+#pragma unroll
+      for (int i = 0; i + 1 < kLead; ++i) fq[i] = fq[i + 1];
+      fetch_next(p, prod, fq[kLead - 1]);
+    }
+    return;
   }
 
-  // ---- per-piece state -------------------------------------------------------------------------
-  uint32_t qf[8][4];   // Q as mma A fragments: 8 k-steps of 16 along head_dim
-  float o[16][4];      // O accumulator: 16 n-blocks of 8 along head_dim
-  float m_run[2], l_run[2];
-  const int qrow0 = lane >> 2;
-  const int qcol = (lane & 3) * 2;
+  // ================================= consumer warps =========================================
+  Walker cons;
+  cons.flat = r_begin;
+  cons.flat_end = r_end;
+  cons.enter(p, start_b, start_page);
+
+  uint32_t qf[NB][8][2];  // Q^T as mma B fragments: 8 k-steps of 16 along head_dim
+  float o[8][NB][4];      // O^T accumulator: 8 M blocks of 16 along head_dim
+  float m_run[NB][2], l_run[NB][2];  // per head column (2 per N block per lane)
+  const int frow = lane >> 2;        // fragment row: token (S^T) or head_dim (O^T) within 8
+  const int fcol = (lane & 3) * 2;   // fragment column pair: head within the N block
+  const int mi = lane >> 3;          // which 8x8 matrix of an ldmatrix.x4 this lane addresses
+  const int lrow = lane & 7;
+  int n_merge = 0;
 
   Tile t;
-  int it = 0;
-  while (cons.next(p, t)) {
+  for (int it = 0; cons.next(p, t); ++it) {
     if (t.first) {
 #pragma unroll
-      for (int nb = 0; nb < 16; ++nb) o[nb][0] = o[nb][1] = o[nb][2] = o[nb][3] = 0.f;
-      m_run[0] = m_run[1] = -INFINITY;
-      l_run[0] = l_run[1] = 0.f;
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) o[j][nb][0] = o[j][nb][1] = o[j][nb][2] = o[j][nb][3] = 0.f;
       const __half* qb = p.q + static_cast<int64_t>(t.b) * p.q_stride_b +
-                         static_cast<int64_t>(head) * p.group * p.q_stride_h;
-      const bool r0ok = qrow0 < p.group;
-      const bool r1ok = (ROWS == 16) && (qrow0 + 8 < p.group);
-      const __half* q0 = qb + static_cast<int64_t>(qrow0) * p.q_stride_h + qcol;
-      const __half* q1 = qb + static_cast<int64_t>(qrow0 + 8) * p.q_stride_h + qcol;
+                         static_cast<int64_t>(head) * p.group * p.q_stride_h + fcol;
 #pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        qf[ks][0] = r0ok ? __ldg(reinterpret_cast<const uint32_t*>(q0 + ks * 16)) : 0u;
-        qf[ks][2] = r0ok ? __ldg(reinterpret_cast<const uint32_t*>(q0 + ks * 16 + 8)) : 0u;
-        qf[ks][1] = r1ok ? __ldg(reinterpret_cast<const uint32_t*>(q1 + ks * 16)) : 0u;
-        qf[ks][3] = r1ok ? __ldg(reinterpret_cast<const uint32_t*>(q1 + ks * 16 + 8)) : 0u;
-      }
-    }
-
-    cp_async_wait<STAGES - 2>();
-    __syncthreads();
-    {  // refill the stage freed by the previous iteration
-      const int ps = (it + STAGES - 1) % STAGES;
-      if (pend_valid) issue_tile(p, head, pend.ntok, pend_base, stage_base + ps * kStageBytes, policy);
-      cp_async_commit();
-      pend_valid = prod.next(p, pend);
-      load_page_bases(p, pend, pend_valid, pend_base);
-    }
-
-    const int wtok0 = warp * 16;
-    if (wtok0 < t.ntok) {
-      const uint32_t ks_smem = stage_base + (it % STAGES) * kStageBytes;
-      const uint32_t vs_smem = ks_smem + kTileBytes;
-      // ---- S = Q K^T over this warp's 16 tokens -----------------------------------------------
-      float s[2][4];
-#pragma unroll
-      for (int nb = 0; nb < 2; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
-      {
-        const int ktok = wtok0 + ((lane >> 4) << 3) + (lane & 7);
-        const uint32_t krow = ks_smem + ktok * kRowBytes;
-        const int kx = ktok & 7;
-        const int csel = (lane >> 3) & 1;
+      for (int nb = 0; nb < NB; ++nb) {
+        m_run[nb][0] = m_run[nb][1] = -INFINITY;
+        l_run[nb][0] = l_run[nb][1] = 0.f;
+        const int hq = nb * 8 + frow;  // B fragment column n = lane / 4
+        const bool hok = hq < p.group;
+        const __half* qh = qb + static_cast<int64_t>(hq) * p.q_stride_h;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          uint32_t kb[4];
-          ldmatrix_x4(kb, krow + (((2 * ks + csel) ^ kx) << 4));
-          mma_16816(s[0], qf[ks], kb[0], kb[1]);
-          mma_16816(s[1], qf[ks], kb[2], kb[3]);
+          qf[nb][ks][0] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16)) : 0u;
+          qf[nb][ks][1] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16 + 8)) : 0u;
         }
       }
-      // ---- online softmax (log2 domain) -----------------------------------------------------
-      // With 8 padded rows the accumulator halves e = 2,3 (rows 8..15) carry no query head.
-      constexpr int kE = (ROWS == 8) ? 2 : 4;
-      float mx[2] = {-INFINITY, -INFINITY};
+    }
+
+    const int st = it % STAGES;
+    if (!mbar_wait_bounded(bar_full + 8 * st, (it / STAGES) & 1)) {
+      set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+      return;
+    }
+
+    const int wtok = t.ntok - warp * kPS;  // valid tokens of this warp's page (may be <= 0)
+#ifdef B200KV_DECODE_PROBE_NO_COMPUTE
+    if (false) {
+#else
+    if (wtok > 0) {
+#endif
+      const uint32_t kpage = stage_base + st * kStageBytes + warp * kPageBytes;
+      const uint32_t vpage = kpage + kTileBytes;
+      if (wtok < kPS) {
+        // Last page of a sequence: its rows past the length were never written and may hold
+        // anything (NaN included); zero them in V so that P = 0 really contributes nothing.
+        for (int i = lane; i < (kPS - wtok) * 16; i += 32) {
+          const int r = wtok + (i >> 4);
+          const int c = i & 15;
+          asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(vpage + page_chunk_off(r, c)),
+                       "r"(0)
+                       : "memory");
+        }
+        fence_proxy_async_smem();  // these generic-proxy writes precede the next TMA refill
+        __syncwarp();
+      }
+      // ---- S^T = K Q^T over this warp's 16 tokens ---------------------------------------------
+      float s[NB][4];
 #pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-        const int col = wtok0 + nb * 8 + qcol;
+      for (int nb = 0; nb < NB; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+      {
+        const int kr = ((mi & 1) << 3) + lrow;  // token row this lane addresses
+        const int csel = mi >> 1;
 #pragma unroll
-        for (int e = 0; e < kE; ++e) {
-          const bool ok = (col + (e & 1)) < t.ntok;
-          s[nb][e] = ok ? s[nb][e] * p.scale_log2 : -INFINITY;
-          mx[e >> 1] = fmaxf(mx[e >> 1], s[nb][e]);
+        for (int ks = 0; ks < 8; ++ks) {
+          uint32_t ka[4];
+          ldmatrix_x4(ka, kpage + page_chunk_off(kr, 2 * ks + csel));
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) mma_16816(s[nb], ka, qf[nb][ks][0], qf[nb][ks][1]);
         }
       }
-      float alpha[2] = {1.f, 1.f}, msub[2] = {0.f, 0.f};
+      // ---- online softmax per head column (log2 domain) ---------------------------------------
+      const bool ok0 = frow < wtok;
+      const bool ok1 = (frow + 8) < wtok;
+      float alpha[NB][2];
+      uint32_t pb[NB][2];
 #pragma unroll
-      for (int r = 0; r < kE / 2; ++r) {
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
-        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float m_new = fmaxf(m_run[r], mx[r]);
-        msub[r] = (m_new == -INFINITY) ? 0.f : m_new;
-        alpha[r] = fast_exp2(m_run[r] - msub[r]);
-        m_run[r] = m_new;
+      for (int nb = 0; nb < NB; ++nb) {
+        float pr[4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float s0 = ok0 ? s[nb][h] * p.scale_log2 : -INFINITY;
+          const float s1 = ok1 ? s[nb][h + 2] * p.scale_log2 : -INFINITY;
+          float mx = fmaxf(s0, s1);
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+          mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+          const float m_new = fmaxf(m_run[nb][h], mx);
+          const float msub = (m_new == -INFINITY) ? 0.f : m_new;
+          alpha[nb][h] = fast_exp2(m_run[nb][h] - msub);
+          m_run[nb][h] = m_new;
+          pr[h] = fast_exp2(s0 - msub);
+          pr[h + 2] = fast_exp2(s1 - msub);
+          l_run[nb][h] = l_run[nb][h] * alpha[nb][h] + pr[h] + pr[h + 2];
+        }
+        // P^T[tok, head] -> B fragment [k = tok, n = head]
+        pb[nb][0] = movmatrix_trans(pack_half2(pr[0], pr[1]));
+        pb[nb][1] = movmatrix_trans(pack_half2(pr[2], pr[3]));
       }
-      uint32_t pf[4];
+      // ---- O^T = alpha * O^T + V^T P^T --------------------------------------------------------
       {
-        float pr[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        float rs[2] = {0.f, 0.f};
+        const int vr = ((mi >> 1) << 3) + lrow;
+        const int csel = mi & 1;
 #pragma unroll
-        for (int nb = 0; nb < 2; ++nb)
+        for (int j = 0; j < 8; ++j) {
+          uint32_t va[4];
+          ldmatrix_x4_trans(va, vpage + page_chunk_off(vr, 2 * j + csel));
 #pragma unroll
-          for (int e = 0; e < kE; ++e) {
-            pr[nb][e] = fast_exp2(s[nb][e] - msub[e >> 1]);
-            rs[e >> 1] += pr[nb][e];
-          }
-        l_run[0] = l_run[0] * alpha[0] + rs[0];
-        l_run[1] = l_run[1] * alpha[1] + rs[1];
-        pf[0] = pack_half2(pr[0][0], pr[0][1]);
-        pf[1] = pack_half2(pr[0][2], pr[0][3]);
-        pf[2] = pack_half2(pr[1][0], pr[1][1]);
-        pf[3] = pack_half2(pr[1][2], pr[1][3]);
-      }
-      // ---- O = alpha * O + P V ----------------------------------------------------------------
-      {
-        const int vtok = wtok0 + (((lane >> 3) & 1) << 3) + (lane & 7);
-        const uint32_t vrow = vs_smem + vtok * kRowBytes;
-        const int vx = vtok & 7;
-        const int csel = lane >> 4;
-#pragma unroll
-        for (int jp = 0; jp < 8; ++jp) {
-          uint32_t vb[4];
-          ldmatrix_x4_trans(vb, vrow + (((2 * jp + csel) ^ vx) << 4));
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            float(&acc)[4] = o[2 * jp + h];
-            acc[0] *= alpha[0];
-            acc[1] *= alpha[0];
-            acc[2] *= alpha[1];
-            acc[3] *= alpha[1];
-            mma_16816(acc, pf, vb[2 * h], vb[2 * h + 1]);
+          for (int nb = 0; nb < NB; ++nb) {
+            float(&acc)[4] = o[j][nb];
+            acc[0] *= alpha[nb][0];
+            acc[1] *= alpha[nb][1];
+            acc[2] *= alpha[nb][0];
+            acc[3] *= alpha[nb][1];
+            mma_16816(acc, va, pb[nb][0], pb[nb][1]);
           }
         }
       }
     }
+    // This warp is done with the stage: hand it back to the producer.
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_empty + 8 * st);
 
     if (t.last) {
       // ---- merge the four warps' (m, l, O) and emit the piece --------------------------------
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
-        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+      if (n_merge > 0 && !mbar_wait_bounded(bar_merge_free, (n_merge - 1) & 1)) {
+        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+        return;
       }
-      float* mo = merge_o + warp * ROWS * kD;
+      float* mo = merge_o + warp * kD * ROWS;
 #pragma unroll
-      for (int nb = 0; nb < 16; ++nb) {
-        const int col = nb * 8 + qcol;
-        *reinterpret_cast<float2*>(mo + qrow0 * kD + col) = make_float2(o[nb][0], o[nb][1]);
-        if (ROWS == 16)
-          *reinterpret_cast<float2*>(mo + (qrow0 + 8) * kD + col) = make_float2(o[nb][2], o[nb][3]);
-      }
-      if ((lane & 3) == 0) {
-        float* ml = merge_ml + warp * ROWS * 2;
-        ml[qrow0 * 2 + 0] = m_run[0];
-        ml[qrow0 * 2 + 1] = l_run[0];
-        if (ROWS == 16) {
-          ml[(qrow0 + 8) * 2 + 0] = m_run[1];
-          ml[(qrow0 + 8) * 2 + 1] = l_run[1];
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float l = l_run[nb][h];
+          l += __shfl_xor_sync(0xffffffffu, l, 4);
+          l += __shfl_xor_sync(0xffffffffu, l, 8);
+          l += __shfl_xor_sync(0xffffffffu, l, 16);
+          if (frow == 0) {
+            float* ml = merge_ml + (warp * ROWS + nb * 8 + fcol + h) * 2;
+            ml[0] = m_run[nb][h];
+            ml[1] = l;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int d0 = j * 16 + frow;
+          *reinterpret_cast<float2*>(mo + d0 * ROWS + nb * 8 + fcol) = make_float2(o[j][nb][0], o[j][nb][1]);
+          *reinterpret_cast<float2*>(mo + (d0 + 8) * ROWS + nb * 8 + fcol) =
+              make_float2(o[j][nb][2], o[j][nb][3]);
         }
       }
-      __syncthreads();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_merge_ready);
+      if (!mbar_wait_bounded(bar_merge_ready, n_merge & 1)) {
+        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+        return;
+      }
       const int64_t slot = (static_cast<int64_t>(team) + t.b) * p.kv_heads + head;
       for (int r = 0; r < p.group; ++r) {
-        float mw[kWarps], M = -INFINITY;
+        float mw[kConsumerWarps], M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
+        for (int w = 0; w < kConsumerWarps; ++w) {
           mw[w] = merge_ml[(w * ROWS + r) * 2];
           M = fmaxf(M, mw[w]);
         }
         float L = 0.f, acc = 0.f;
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
+        for (int w = 0; w < kConsumerWarps; ++w) {
           const float sc = (mw[w] == -INFINITY) ? 0.f : fast_exp2(mw[w] - M);
           L += sc * merge_ml[(w * ROWS + r) * 2 + 1];
-          acc += sc * merge_o[(w * ROWS + r) * kD + tid];
+          acc += sc * merge_o[(w * kD + tid) * ROWS + r];
         }
         const float val = acc / L;
         if (t.whole) {
@@ -465,21 +564,25 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) paged_decode_split_kerne
           if (tid == 0) p.part_lse[slot * ROWS + r] = M + log2f(L);
         }
       }
-      // the next write to the merge buffer is at least one __syncthreads away (loop top)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_merge_free);
+      ++n_merge;
     }
-    ++it;
   }
-  cp_async_wait<0>();
 }
 
 // Merge the split partials of each sequence: out = sum_p 2^(lse_p - M) o_p / sum_p 2^(lse_p - M)
 // (stage 2 of the reference, lite_llama/kernels/flashdecoding.py:199-267).  One CTA per
-// sequence, one warp per query head at a time; lanes hold the pieces' log-sum-exp values and
-// reduce them with warp shuffles, then every lane accumulates four output columns.
+// (sequence, KV head), one warp per query head of the group at a time; lanes hold the pieces'
+// log-sum-exp values and reduce them with warp shuffles, then every lane accumulates four
+// output columns.  Launched with programmatic stream serialisation: everything up to
+// cudaGridDependencySynchronize() (recomputing which teams touched this sequence) overlaps
+// the tail of the split kernel.
 template <int ROWS>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeParams p) {
   __shared__ long long red[2][kCombineThreads / 32];
-  const int b = blockIdx.x;
+  const int b = blockIdx.x / p.kv_heads;
+  const int kvh = blockIdx.x - b * p.kv_heads;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
@@ -508,11 +611,12 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   }
 
   const int len = seq_len_checked(p, b);
-  if (len == 0) {  // no keys: the output row is defined as zero
-    for (int i = tid; i < p.q_heads * kD; i += kCombineThreads) {
-      const int h = i / kD;
-      p.out[static_cast<int64_t>(b) * p.out_stride_b + static_cast<int64_t>(h) * p.out_stride_h +
-            (i - h * kD)] = __float2half_rn(0.f);
+  if (len == 0) {  // no keys: the output rows are defined as zero (nobody else writes them)
+    for (int i = tid; i < p.group * kD; i += kCombineThreads) {
+      const int g = i / kD;
+      p.out[static_cast<int64_t>(b) * p.out_stride_b +
+            (static_cast<int64_t>(kvh) * p.group + g) * p.out_stride_h + (i - g * kD)] =
+          __float2half_rn(0.f);
     }
     return;
   }
@@ -521,11 +625,12 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   const int t_first = team_of(before, nteams_eff, total);
   const int t_last = team_of(before + np - 1, nteams_eff, total);
   const int npieces = t_last - t_first + 1;
-  if (npieces == 1) return;  // the split kernel already wrote the final row
+  if (npieces == 1) return;  // the split kernel wrote the final rows itself
 
-  for (int hq = warp; hq < p.q_heads; hq += kCombineThreads / 32) {
-    const int kvh = hq / p.group;
-    const int g = hq - kvh * p.group;
+  cudaGridDependencySynchronize();  // partials of the split kernel are visible from here on
+
+  for (int g = warp; g < p.group; g += kCombineThreads / 32) {
+    const int hq = kvh * p.group + g;
     float M = -INFINITY;
     for (int p0 = 0; p0 < npieces; p0 += 32) {
       const int pc = p0 + lane;
@@ -579,8 +684,10 @@ inline int max_teams(int sms, int kv_heads) {
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 template <int ROWS, int STAGES>
-int launch_decode(const DecodeParams& p, cudaStream_t stream) {
-  constexpr int smem = STAGES * kStageBytes + kWarps * ROWS * kD * 4 + kWarps * ROWS * 2 * 4;
+int launch_decode(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                  cudaStream_t stream) {
+  constexpr int smem = STAGES * kStageBytes + kConsumerWarps * ROWS * kD * 4 +
+                       kConsumerWarps * ROWS * 2 * 4 + (2 * STAGES + 2) * 8;
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return record_cuda_error(cudaGetLastError());
@@ -591,10 +698,21 @@ int launch_decode(const DecodeParams& p, cudaStream_t stream) {
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
   paged_decode_split_kernel<ROWS, STAGES>
-      <<<static_cast<unsigned>(p.nteams * p.kv_heads), kThreads, smem, stream>>>(p);
+      <<<static_cast<unsigned>(p.nteams * p.kv_heads), kThreads, smem, stream>>>(p, kmap, vmap);
   int rc = check_launch();
   if (rc != B200KV_OK) return rc;
-  decode_combine_kernel<ROWS><<<static_cast<unsigned>(p.batch), kCombineThreads, 0, stream>>>(p);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.batch * p.kv_heads));
+  cfg.blockDim = dim3(kCombineThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_combine_kernel<ROWS>, p);
+  if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
 
@@ -674,8 +792,17 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.out_stride_h = a.out_stride_h;
   p.status = a.status;
 
-  if (rows == 8) return launch_decode<8, 3>(p, stream);
-  return launch_decode<16, 2>(p, stream);
+  // TMA views of the K and V halves of the pool (d, head, token); one box = 16 token rows of
+  // 64 halves, i.e. half a page of one head.
+  CUtensorMap kmap, vmap;
+  int rc = encode_kv_tensor_map(&kmap, a.k_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+                                a.kv_heads, kD, kPS);
+  if (rc != B200KV_OK) return rc;
+  rc = encode_kv_tensor_map(&vmap, a.v_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+                            a.kv_heads, kD, kPS);
+  if (rc != B200KV_OK) return rc;
+  if (rows == 8) return launch_decode<8, kStagesRows8>(p, kmap, vmap, stream);
+  return launch_decode<16, 2>(p, kmap, vmap, stream);
 }
 
 }  // namespace b200kv

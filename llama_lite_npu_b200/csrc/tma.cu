@@ -1,0 +1,61 @@
+// cuTensorMapEncodeTiled is a driver-API entry point; it is resolved through the runtime
+// (cudaGetDriverEntryPoint) so the library links against libcudart only.
+#include "tma.h"
+
+#include <cstdio>
+
+#include "b200kv.h"
+#include "launch.h"
+
+namespace b200kv {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      record_cuda_error(e != cudaSuccess ? e : cudaErrorSymbolNotFound);
+      return static_cast<EncodeTiledFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+}  // namespace
+
+int encode_kv_tensor_map(CUtensorMap* out, const void* base, int64_t pool_tokens,
+                         int64_t tok_stride, int64_t head_stride, int n_heads, int head_dim,
+                         int box_tokens) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return B200KV_ECUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0) return B200KV_EALIGN;
+  if ((tok_stride * 2) % 16 != 0 || (head_stride * 2) % 16 != 0) return B200KV_EALIGN;
+  if (pool_tokens <= 0 || n_heads <= 0 || head_dim % 64 != 0 || box_tokens <= 0 || box_tokens > 256)
+    return B200KV_EINVAL;
+  // Dimensions fastest first: d, head, token.
+  const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(n_heads),
+                              static_cast<cuuint64_t>(pool_tokens)};
+  const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(head_stride) * 2,
+                                 static_cast<cuuint64_t>(tok_stride) * 2};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_tokens)};
+  const cuuint32_t estride[3] = {1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), gdim, gstride,
+                  box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    record_cuda_error(cudaErrorInvalidValue);
+    return B200KV_ECUDA;
+  }
+  return B200KV_OK;
+}
+
+}  // namespace b200kv
