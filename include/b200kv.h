@@ -18,6 +18,15 @@
  * is recorded in *status (a device int32 the caller zeroes beforehand and may
  * read back whenever it is willing to synchronise).
  *
+ * Stream ordering: kernels are launched with programmatic stream serialisation
+ * (programmatic dependent launch).  Each kernel touches q / K / V / the pool /
+ * workspaces / outputs only after the previous kernel in the stream has
+ * completed, but the split-KV decode kernel plans its work (reads seq_lens,
+ * row_ids and the page table) before that point, overlapping the tail of the
+ * previous kernel.  Those three metadata arrays must therefore not be produced
+ * by the kernel launched IMMEDIATELY before b200kv_paged_decode on the same
+ * stream; anything earlier (copies, other kernels) is ordered as usual.
+ *
  * The reference project (lite_llama, Python + Triton-Ascend) has no native
  * interface; each function below names the reference Python operator whose
  * device work it replaces, as file:line inside that project.

@@ -32,6 +32,10 @@ struct AppendParams {
 };
 
 __global__ void __launch_bounds__(kAppendThreads) kv_append_kernel(AppendParams p) {
+  // Programmatic dependent launch: this kernel has no prologue worth overlapping, so it waits
+  // for the previous kernel first and only then lets its own dependent start its prologue.
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
   const int64_t total = p.n_tokens * p.vec_per_token;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * kAppendThreads;
   int64_t i = static_cast<int64_t>(blockIdx.x) * kAppendThreads + threadIdx.x;
@@ -74,7 +78,17 @@ int launch_append(AppendParams p, cudaStream_t stream) {
   int64_t blocks = (total + kAppendThreads * kAppendUnroll - 1) / (kAppendThreads * kAppendUnroll);
   const int64_t cap = static_cast<int64_t>(sms) * 8;  // 8 resident CTAs of 256 threads per SM
   if (blocks > cap) blocks = cap;
-  kv_append_kernel<<<static_cast<unsigned>(blocks), kAppendThreads, 0, stream>>>(p);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+  cfg.blockDim = dim3(kAppendThreads);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kv_append_kernel, p);
+  if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
 

@@ -192,6 +192,17 @@ __device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fet
   }
 }
 
+// Programmatic dependent launch, used by every kernel of this library the same way: whatever
+// a kernel does BEFORE this call may overlap the tail of the previous kernel in the stream, so
+// it must only read launch metadata (lengths, row ids, page table) that an earlier, already
+// completed operation produced.  Releasing our own dependents only after our own wait keeps the
+// guarantee transitive: when a dependent's prologue runs, everything two or more kernels back
+// has completed.
+__device__ __forceinline__ void pdl_wait_then_trigger() {
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
+}
+
 // Transpose an 8x8 matrix of b16 held in mma-fragment layout (lane l: row l/4, cols 2(l%4)..+1).
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t d;
@@ -234,10 +245,6 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const int warp = tid >> 5;
   const int team = blockIdx.x / p.kv_heads;
   const int head = blockIdx.x - team * p.kv_heads;
-  // Let the merge kernel be scheduled behind us right away; it waits for this whole grid with
-  // cudaGridDependencySynchronize() before touching any partial.
-  cudaTriggerProgrammaticLaunchCompletion();
-
   const uint32_t stage_base = smem_u32(stages);
   const uint32_t bar_full = smem_u32(bars);                 // [STAGES]
   const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
@@ -334,6 +341,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     Fetch fq[kLead];
 #pragma unroll
     for (int i = 0; i < kLead; ++i) fetch_next(p, prod, fq[i]);
+    pdl_wait_then_trigger();  // the pool may have been written by the previous kernel
     const int my_page = lane >> 2;
     const int my_part = lane & 3;
     const CUtensorMap* my_map = (my_part & 2) ? &vmap : &kmap;
@@ -386,6 +394,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const int mi = lane >> 3;          // which 8x8 matrix of an ldmatrix.x4 this lane addresses
   const int lrow = lane & 7;
   int n_merge = 0;
+  pdl_wait_then_trigger();  // q, the workspace and out belong to earlier kernels until here
 
   Tile t;
   for (int it = 0; cons.next(p, t); ++it) {
@@ -575,9 +584,9 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
 // (stage 2 of the reference, lite_llama/kernels/flashdecoding.py:199-267).  One CTA per
 // (sequence, KV head), one warp per query head of the group at a time; lanes hold the pieces'
 // log-sum-exp values and reduce them with warp shuffles, then every lane accumulates four
-// output columns.  Launched with programmatic stream serialisation: everything up to
-// cudaGridDependencySynchronize() (recomputing which teams touched this sequence) overlaps
-// the tail of the split kernel.
+// output columns.  Launched with programmatic stream serialisation: everything before
+// pdl_wait_then_trigger() (recomputing which teams touched this sequence) overlaps the tail
+// of the split kernel.
 template <int ROWS>
 __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeParams p) {
   __shared__ long long red[2][kCombineThreads / 32];
@@ -612,6 +621,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
 
   const int len = seq_len_checked(p, b);
   if (len == 0) {  // no keys: the output rows are defined as zero (nobody else writes them)
+    pdl_wait_then_trigger();
     for (int i = tid; i < p.group * kD; i += kCombineThreads) {
       const int g = i / kD;
       p.out[static_cast<int64_t>(b) * p.out_stride_b +
@@ -627,10 +637,43 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   const int npieces = t_last - t_first + 1;
   if (npieces == 1) return;  // the split kernel wrote the final rows itself
 
-  cudaGridDependencySynchronize();  // partials of the split kernel are visible from here on
+  pdl_wait_then_trigger();  // partials of the split kernel are visible from here on
 
   for (int g = warp; g < p.group; g += kCombineThreads / 32) {
     const int hq = kvh * p.group + g;
+    if (npieces <= 4) {
+      // Common case: issue the loads of every piece's log-sum-exp AND output together, so the
+      // merge costs one memory round trip instead of two.
+      float lse[4];
+      float4 ov[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int64_t slot = (static_cast<int64_t>(t_first + min(j, npieces - 1)) + b) * p.kv_heads + kvh;
+        lse[j] = (j < npieces) ? p.part_lse[slot * ROWS + g] : -INFINITY;
+        ov[j] = *reinterpret_cast<const float4*>(p.part_o + (slot * ROWS + g) * kD + lane * 4);
+      }
+      const float M4 = fmaxf(fmaxf(lse[0], lse[1]), fmaxf(lse[2], lse[3]));
+      float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+      float wsum4 = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w = (j < npieces) ? fast_exp2(lse[j] - M4) : 0.f;
+        wsum4 += w;
+        acc4.x += w * ov[j].x;
+        acc4.y += w * ov[j].y;
+        acc4.z += w * ov[j].z;
+        acc4.w += w * ov[j].w;
+      }
+      const float inv4 = 1.f / wsum4;
+      __half2 a01 = __floats2half2_rn(acc4.x * inv4, acc4.y * inv4);
+      __half2 a23 = __floats2half2_rn(acc4.z * inv4, acc4.w * inv4);
+      uint2 pk4;
+      pk4.x = *reinterpret_cast<uint32_t*>(&a01);
+      pk4.y = *reinterpret_cast<uint32_t*>(&a23);
+      *reinterpret_cast<uint2*>(p.out + static_cast<int64_t>(b) * p.out_stride_b +
+                                static_cast<int64_t>(hq) * p.out_stride_h + lane * 4) = pk4;
+      continue;
+    }
     float M = -INFINITY;
     for (int p0 = 0; p0 < npieces; p0 += 32) {
       const int pc = p0 + lane;
@@ -697,21 +740,24 @@ int launch_decode(const DecodeParams& p, const CUtensorMap& kmap, const CUtensor
     if (e != cudaSuccess) return record_cuda_error(e);
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
   }
-  paged_decode_split_kernel<ROWS, STAGES>
-      <<<static_cast<unsigned>(p.nteams * p.kv_heads), kThreads, smem, stream>>>(p, kmap, vmap);
-  int rc = check_launch();
-  if (rc != B200KV_OK) return rc;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(p.batch * p.kv_heads));
-  cfg.blockDim = dim3(kCombineThreads);
-  cfg.dynamicSmemBytes = 0;
-  cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(p.nteams * p.kv_heads));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_combine_kernel<ROWS>, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, paged_decode_split_kernel<ROWS, STAGES>, p, kmap, vmap);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  int rc = check_launch();
+  if (rc != B200KV_OK) return rc;
+  cfg.gridDim = dim3(static_cast<unsigned>(p.batch * p.kv_heads));
+  cfg.blockDim = dim3(kCombineThreads);
+  cfg.dynamicSmemBytes = 0;
+  e = cudaLaunchKernelEx(&cfg, decode_combine_kernel<ROWS>, p);
   if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
