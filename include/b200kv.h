@@ -147,6 +147,46 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                         int32_t* status, void* stream);
 
 /*
+ * Paged flash-decoding for callers that cannot allocate device memory.
+ * (No counterpart in the reference: its decode operator allocates its partial
+ * buffers with torch on every call.)
+ *
+ * Identical to b200kv_paged_decode in arguments, semantics and results, except
+ * that there is no workspace argument: the split-KV partials go to a fixed
+ * array of B200KV_STATIC_SCRATCH_BYTES that is part of the library image on
+ * every GPU that loads it.  Meant for hosts that have no way to get device
+ * memory when the call is made -- a server whose device budget was handed to
+ * one arena at start-up and which treats any later cudaMalloc as an error, a
+ * plug-in whose memory is owned by the embedding application, a real-time loop
+ * that cannot risk the device-wide stall an allocation or free can cause.  The
+ * call path contains no cudaMalloc / cudaFree and no allocating library call.
+ *
+ * Limits and rules:
+ *  - the batch must be small enough that b200kv_decode_workspace_bytes() for it
+ *    is <= B200KV_STATIC_SCRATCH_BYTES; larger batches are refused with
+ *    B200KV_ETOOLARGE before anything is launched (split the batch, or use
+ *    b200kv_paged_decode with a caller-owned workspace);
+ *  - the first call on each device looks up the array's device address (with
+ *    that device current) and should be made before any stream capture begins;
+ *  - all calls on one device share the one array, which keeps whatever the last
+ *    call left there.  Nothing in it needs to start at zero (every partial is
+ *    written before it is read), but two calls whose kernels may overlap on the
+ *    GPU -- different streams without an ordering between them -- race on it.
+ */
+#define B200KV_STATIC_SCRATCH_BYTES (8u << 20)
+int b200kv_paged_decode_static_scratch(
+    const void* q, int64_t q_stride_b, int64_t q_stride_h,
+    const void* k_base, const void* v_base,
+    int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
+    const int32_t* table, int64_t table_row_stride, int table_kind,
+    const int32_t* row_ids,
+    const void* seq_lens, int seq_lens_i64,
+    int batch, int q_heads, int kv_heads, int head_dim, int page_size,
+    float scale, int64_t max_seq_len,
+    void* out, int64_t out_stride_b, int64_t out_stride_h,
+    int32_t* status, void* stream);
+
+/*
  * Packed no-pad causal prefill over paged KV with history: query row i of
  * request r sits at logical position ctx_r + i and sees keys 0..ctx_r+i of
  * that request's table row.  Replaces paged_chunk_flash_attention

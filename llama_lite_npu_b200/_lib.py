@@ -42,6 +42,18 @@ _SIGNATURES = {
          c_void_p, c_int64, c_int64,             # out
          c_void_p, c_void_p],                    # status, stream
     ),
+    "b200kv_paged_decode_static_scratch": (
+        c_int,
+        [c_void_p, c_int64, c_int64,
+         c_void_p, c_void_p, c_int64, c_int64, c_int64,
+         c_void_p, c_int64, c_int,
+         c_void_p,
+         c_void_p, c_int,
+         c_int, c_int, c_int, c_int, c_int,
+         c_float, c_int64,
+         c_void_p, c_int64, c_int64,
+         c_void_p, c_void_p],
+    ),
     "b200kv_paged_prefill": (
         c_int,
         [c_void_p, c_int64, c_int64,

@@ -125,6 +125,44 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, c
   return b200kv::paged_decode(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_paged_decode_static_scratch(
+    const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_base, const void* v_base,
+    int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens, const int32_t* table,
+    int64_t table_row_stride, int table_kind, const int32_t* row_ids, const void* seq_lens,
+    int seq_lens_i64, int batch, int q_heads, int kv_heads, int head_dim, int page_size, float scale,
+    int64_t max_seq_len, void* out, int64_t out_stride_b, int64_t out_stride_h, int32_t* status,
+    void* stream) {
+  b200kv::DecodeArgs a{};
+  a.q = q;
+  a.q_stride_b = q_stride_b;
+  a.q_stride_h = q_stride_h;
+  a.k_base = k_base;
+  a.v_base = v_base;
+  a.kv_tok_stride = kv_tok_stride;
+  a.kv_head_stride = kv_head_stride;
+  a.pool_tokens = pool_tokens;
+  a.table = table;
+  a.table_row_stride = table_row_stride;
+  a.table_kind = table_kind;
+  a.row_ids = row_ids;
+  a.seq_lens = seq_lens;
+  a.seq_lens_i64 = seq_lens_i64;
+  a.batch = batch;
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.page_size = page_size;
+  a.scale = scale;
+  a.max_seq_len = max_seq_len;
+  a.workspace = nullptr;
+  a.workspace_bytes = 0;
+  a.out = out;
+  a.out_stride_b = out_stride_b;
+  a.out_stride_h = out_stride_h;
+  a.status = status;
+  return b200kv::paged_decode_static_scratch(a, static_cast<cudaStream_t>(stream));
+}
+
 int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k_base,
                          const void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
                          int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,

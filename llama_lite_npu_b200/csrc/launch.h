@@ -44,6 +44,8 @@ struct DecodeArgs {
 };
 size_t decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim);
 int paged_decode(const DecodeArgs& a, cudaStream_t stream);
+// Same, with the split-KV scratch in a fixed device array owned by the library (args.workspace ignored).
+int paged_decode_static_scratch(const DecodeArgs& args, cudaStream_t stream);
 
 struct PrefillArgs {
   const void* q;

@@ -851,4 +851,39 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   return launch_decode<16, 2>(p, kmap, vmap, stream);
 }
 
+// ---- decode on library-owned scratch (no allocation anywhere on the call path) -----------------
+//
+// Some hosts cannot hand us a workspace because they cannot obtain device memory at call time at
+// all: a serving process that gave its whole device budget to one arena at start-up and treats a
+// later cudaMalloc as a fault; a plug-in whose device memory is accounted for by the embedding
+// application; code running where the CUDA allocator must not be entered (a latency-critical
+// loop that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply).  For them
+// the split-KV partials live in this file-scope device array instead.  Every GPU that loads the
+// library holds these bytes until the process exits, which is why the size is modest and fixed.
+constexpr size_t kStaticScratchBytes = B200KV_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+int paged_decode_static_scratch(const DecodeArgs& args, cudaStream_t stream) {
+  if (args.batch < 0) return B200KV_EINVAL;
+  if (args.batch == 0) return B200KV_OK;
+  const size_t need = decode_workspace_bytes(args.batch, args.q_heads, args.kv_heads, args.head_dim);
+  if (need > kStaticScratchBytes) return B200KV_ETOOLARGE;  // need == 0: rejected below with its own code
+  // In host code `g_decode_scratch` is only a handle for the symbol, not an address the GPU
+  // understands; the device address is asked for once per device, with that device current.
+  static void* scratch_of_device[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return record_cuda_error(cudaGetLastError());
+  if (dev < 0 || dev >= 64) return B200KV_EUNSUPPORTED;
+  if (scratch_of_device[dev] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+    if (e != cudaSuccess || ptr == nullptr) return record_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    scratch_of_device[dev] = ptr;
+  }
+  DecodeArgs a = args;
+  a.workspace = scratch_of_device[dev];
+  a.workspace_bytes = kStaticScratchBytes;
+  return paged_decode(a, stream);
+}
+
 }  // namespace b200kv
