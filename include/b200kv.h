@@ -68,6 +68,9 @@ extern "C" {
  *        entries at t % page_size == 0 are read. */
 #define B200KV_TABLE_BLOCK 0
 #define B200KV_TABLE_TOKEN 1
+/* DENSE (prefill only): no table; logical token t of request r is slot
+ * q_start[r] + t of k_base / v_base, i.e. K/V are packed exactly like Q. */
+#define B200KV_TABLE_DENSE 2
 
 int b200kv_version(void);
 const char* b200kv_strerror(int code);

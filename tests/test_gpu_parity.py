@@ -202,3 +202,157 @@ def test_decode_c2_full_size_properties():
     out_c = kernels.flash_decoding(c.q, c.k_cache, c.v_cache, SCALE, c.block_table, c.seq_lens_t,
                                    c.max_len, table_kind="block")
     assert _maxdiff(out_c, torch.full_like(out_c, 0.5)) <= 1e-3
+
+
+# ---- packed prefill over paged KV (tcgen05) --------------------------------------------------
+LOG2E = 1.4426950408889634
+
+
+def _prefill_gpu(c, table_kind="token"):
+    """Append the chunk's K/V, then attend (what Attention.context_forward does)."""
+    kh = c.cfg.kv_heads
+    pool_d = c.pool.to(DEV)
+    kernels.update_kv_buffer(c.new_kv.to(DEV), c.slots.to(DEV), pool_d)
+    tbl = (c.token_table if table_kind == "token" else c.block_table).to(DEV)
+    out = kernels.paged_chunk_flash_attention(
+        c.q.to(DEV), pool_d[:, :kh], pool_d[:, kh:], SCALE * LOG2E, tbl, c.req_ids.to(DEV),
+        c.q_start.to(DEV), c.ctx_lens_t.to(DEV), c.q_lens_t.to(DEV), c.max_q_len, table_kind=table_kind)
+    return out, pool_d
+
+
+def _prefill_oracle(c):
+    kh = c.cfg.kv_heads
+    pool = c.pool.clone()
+    O.kv_append(c.new_kv, c.slots, pool)
+    return O.paged_attention(c.q, pool[:, :kh], pool[:, kh:], SCALE, c.token_table, c.req_ids,
+                             c.q_start, c.ctx_lens_t, c.q_lens_t)
+
+
+@pytest.mark.parametrize("name", list(G.PREFILL_CASES))
+@pytest.mark.parametrize("table_kind", ["token", "block"])
+def test_prefill_with_history_matches_golden_and_oracle(name, table_kind, golden):
+    c = G.build_prefill(name)
+    got, _ = _prefill_gpu(c, table_kind)
+    ref = torch.from_numpy(golden["arrays"][name])
+    assert _maxdiff(got, ref) <= ATTN_TOL
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+def test_prefill_boundary_lengths():
+    """Query lengths around the 128-row tile and the 64-key tile, contexts around page/tile edges."""
+    prompts = [1, 2, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 192, 193, 257, 300]
+    shared = [0, 0, 0, 0, 1, 3, 3, 4, 7, 7, 8, 0, 11, 4, 16, 2]
+    cfg = W.PrefillConfig("prefill_bounds", len(prompts), 4, 2, 512, 1, 1, seed=91)
+    c = W.make_prefill_case(cfg, fill="hash", prompt_lens=np.array(prompts), shared_pages=np.array(shared))
+    got, _ = _prefill_gpu(c, "block")
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+@pytest.mark.parametrize("group,kvh", [(1, 2), (4, 2), (8, 1), (16, 1)])
+def test_prefill_group_sizes_int32_lengths(group, kvh):
+    cfg = W.PrefillConfig(f"pg{group}", 3, group * kvh, kvh, 256, 1, 1, seed=92 + group)
+    c = W.make_prefill_case(cfg, fill="hash", prompt_lens=np.array([70, 333, 150]),
+                            shared_pages=np.array([2, 9, 0]))
+    kh = cfg.kv_heads
+    pool_d = c.pool.to(DEV)
+    kernels.update_kv_buffer(c.new_kv.to(DEV), c.slots.to(DEV), pool_d)
+    got = kernels.paged_chunk_flash_attention(
+        c.q.to(DEV), pool_d[:, :kh], pool_d[:, kh:], SCALE * LOG2E, c.block_table.to(DEV),
+        c.req_ids.to(DEV), c.q_start.to(DEV), c.ctx_lens_t.int().to(DEV), c.q_lens_t.int().to(DEV),
+        c.max_q_len, table_kind="block")
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+def test_prefill_request_rows_permuted():
+    """req_ids select table rows; the packed order of requests is independent of their rows."""
+    c = G.build_prefill("prefill_hist_gqa2")
+    perm = torch.tensor([2, 0, 1])
+    table = torch.zeros(4, c.block_table.shape[1], dtype=torch.int32)
+    table[perm] = c.block_table
+    kh = c.cfg.kv_heads
+    pool_d = c.pool.to(DEV)
+    kernels.update_kv_buffer(c.new_kv.to(DEV), c.slots.to(DEV), pool_d)
+    got = kernels.paged_chunk_flash_attention(
+        c.q.to(DEV), pool_d[:, :kh], pool_d[:, kh:], SCALE * LOG2E, table.to(DEV), perm.int().to(DEV),
+        c.q_start.to(DEV), c.ctx_lens_t.to(DEV), c.q_lens_t.to(DEV), c.max_q_len, table_kind="block")
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+@pytest.mark.parametrize("name", list(G.NOPAD_CASES))
+def test_nopad_prefill_matches_reference_and_paged_statement(name, golden):
+    q, k, v, start, lens = G.build_nopad(name)
+    got = kernels.flash_attention2_no_pad(q.to(DEV), k.to(DEV), v.to(DEV), SCALE * LOG2E,
+                                          start.to(DEV), lens.to(DEV), int(lens.max()))
+    width = int(lens.max())
+    table = (start[:, None] + torch.arange(width)[None, :]).int()
+    want = O.paged_attention(q, k, v, SCALE, table, torch.arange(len(lens)), start,
+                             torch.zeros_like(lens), lens)
+    assert _maxdiff(got, want) <= ATTN_TOL
+    # the reference's torch statement of this operator rounds the scores to fp16 first
+    ref = torch.from_numpy(golden["arrays"][name])
+    assert _maxdiff(got, ref) <= 4e-3
+
+
+def test_nopad_prefill_gqa_dense():
+    lens = [130, 64, 257]
+    total = sum(lens)
+    q = W.hash_normal_fp16(95, (total, 8, 128), 1)
+    k = W.hash_normal_fp16(95, (total, 2, 128), 2)
+    v = W.hash_normal_fp16(95, (total, 2, 128), 3)
+    start = torch.tensor([0, 130, 194], dtype=torch.int32)
+    lens_t = torch.tensor(lens, dtype=torch.int64)
+    got = kernels.flash_attention2_no_pad(q.to(DEV), k.to(DEV), v.to(DEV), SCALE * LOG2E,
+                                          start.to(DEV), lens_t.to(DEV), max(lens))
+    table = (start[:, None] + torch.arange(max(lens))[None, :]).int()
+    want = O.paged_attention(q, k, v, SCALE, table, torch.arange(3), start, torch.zeros(3, dtype=torch.int64), lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
+
+
+def test_prefill_garbage_in_unwritten_slots_is_harmless():
+    """NaN in pool slots past each sequence's length (same page) must not reach the output."""
+    c = G.build_prefill("prefill_hist_gqa8_edges")
+    used = torch.zeros(c.pool.shape[0], dtype=torch.bool)
+    for i in range(c.cfg.batch):
+        used[c.token_table[i, : int(c.prompt_lens[i])].long()] = True
+    c.pool[~used] = float("nan")
+    got, _ = _prefill_gpu(c, "block")
+    assert not bool(torch.isnan(got).any())
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+def test_decode_garbage_in_unwritten_slots_is_harmless():
+    c = G.build_decode("decode_gqa4_edges")
+    used = torch.zeros(c.pool.shape[0], dtype=torch.bool)
+    for i in range(c.cfg.batch):
+        used[c.token_table[i, : int(c.seq_lens[i])].long()] = True
+    c.pool[~used] = float("nan")
+    got = _decode_gpu(c, "block")
+    assert not bool(torch.isnan(got).any())
+    want = O.paged_decode(c.q, torch.nan_to_num(c.k_cache), torch.nan_to_num(c.v_cache), SCALE,
+                          c.token_table, c.seq_lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
+
+
+def test_prefill_c4_full_size_properties():
+    """Config C4 at full size (8 prompts of 128..2048 tokens, 64/8 heads, 0-50 % shared prefix
+    pages): the suffix K/V append is bit-exact, two sampled requests equal the oracle, and a
+    uniform V gives that constant back."""
+    c = W.make_prefill_case(W.C4, fill="hash")
+    got, pool_d = _prefill_gpu(c, "block")
+    want_pool = c.pool.clone()
+    O.kv_append(c.new_kv, c.slots, want_pool)
+    assert torch.equal(pool_d.cpu(), want_pool)
+    assert int((c.page_refcount == 2).sum()) == int((c.ctx_lens // 16).sum())
+    order = np.argsort(c.q_lens)
+    for b in (int(order[0]), int(order[len(order) // 2])):
+        s, n = int(c.q_start[b]), int(c.q_lens[b])
+        want = O.paged_attention(c.q[s: s + n], want_pool[:, :8], want_pool[:, 8:], SCALE, c.token_table,
+                                 c.req_ids[b: b + 1], torch.zeros(1, dtype=torch.int32),
+                                 c.ctx_lens_t[b: b + 1], c.q_lens_t[b: b + 1])
+        assert _maxdiff(got[s: s + n], want) <= ATTN_TOL
+    pool_d[:, 8:] = 0.25
+    out_c = kernels.paged_chunk_flash_attention(
+        c.q.to(DEV), pool_d[:, :8], pool_d[:, 8:], SCALE * LOG2E, c.block_table.to(DEV),
+        c.req_ids.to(DEV), c.q_start.to(DEV), c.ctx_lens_t.to(DEV), c.q_lens_t.to(DEV), c.max_q_len,
+        table_kind="block")
+    assert _maxdiff(out_c, torch.full_like(out_c, 0.25)) <= 1e-3
