@@ -44,7 +44,7 @@ L2_BYTES = 126 * 1024 * 1024
 GRAPH_STEPS = 64   # layer steps captured per CUDA graph (a 64-layer model's decode pass)
 # "c2s" is the C2 shape on a 1 GiB pool: small enough for multi-pass ncu captures.
 C2_SMALL_POOL = W.DecodeConfig("c2_qwen3_32b_decode_smallpool", 32, 64, 8, 16384, 1024, 4096, seed=1002)
-WORKLOADS = {"c1": W.C1, "c2": W.C2, "c2s": C2_SMALL_POOL, "c3": W.C3, "c5": W.C5}
+WORKLOADS = {"c1": W.C1, "c2": W.C2, "c2s": C2_SMALL_POOL, "c3": W.C3, "c4": W.C4, "c5": W.C5}
 
 
 def dist_env():
@@ -391,15 +391,151 @@ def run_b200(args, cfg_full):
         dist.destroy_process_group()
 
 
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
+# the ncu captures summarised under profiles/.  The decode capture ran on the small-pool twin of
+# the Qwen3-32B workload (identical sequences and lengths, so identical traffic).
+NCU_TRAFFIC_BYTES = {
+    "c2_qwen3_32b_decode": 345.7e6,
+    "c2_qwen3_32b_decode_smallpool": 345.7e6,
+}
+
+
 def ncu_traffic(workload: str, world: int):
-    """DRAM bytes per launch of the split-KV kernel from the committed ncu summary, if any."""
-    p = ROOT / "profiles" / "traffic.json"
-    if world == 1 and p.exists():
-        try:
-            return json.loads(p.read_text()).get(workload)
-        except Exception:
-            return None
-    return None
+    return NCU_TRAFFIC_BYTES.get(workload) if world == 1 else None
+
+
+# ------------------------------------------------------------------------------------------
+# Prefill workload (config C4): suffix KV append + packed causal prefill over paged KV
+# ------------------------------------------------------------------------------------------
+def run_prefill(args, cfg_full):
+    from llama_lite_npu_b200 import _lib, kernels
+
+    rank, local_rank, world = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device")
+    _lib.lib()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    cfg = W.shard_kv_heads(cfg_full, world, rank) if world > 1 else cfg_full
+    kvh = cfg.kv_heads
+    scale_log2 = 1.4426950408889634 / math.sqrt(cfg.head_dim)
+    case = W.make_prefill_case(cfg, device="cpu", fill="hash")
+    for name in ("pool", "block_table", "req_ids", "q_start", "ctx_lens_t", "q_lens_t", "q", "new_kv", "slots"):
+        setattr(case, name, getattr(case, name).to(dev))
+    flops = case.flops()
+    stream = torch.cuda.Stream()
+
+    def attend():
+        return kernels.paged_chunk_flash_attention(
+            case.q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
+            case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
+
+    def step(_i=0):
+        kernels.update_kv_buffer(case.new_kv, case.slots, case.pool)
+        return attend()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        kernels.check_status(local_rank)
+
+        def timed(fn, k):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                fn()
+            g.replay()
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record(stream)
+            for _ in range(k):
+                g.replay()
+            t1.record(stream)
+            barrier()
+            return t0.elapsed_time(t1) / k
+
+        if sampler:
+            sampler.__enter__()
+        ms_step = timed(step, args.steps)
+        ms_kernel = timed(attend, args.steps)
+        h_q, h_kv = case.q.cpu().pin_memory(), case.new_kv.cpu().pin_memory()
+        h_out = torch.empty_like(h_q).pin_memory()
+        d_q, d_kv = torch.empty_like(case.q), torch.empty_like(case.new_kv)
+
+        def e2e_step():
+            d_q.copy_(h_q, non_blocking=True)
+            d_kv.copy_(h_kv, non_blocking=True)
+            kernels.update_kv_buffer(d_kv, case.slots, case.pool)
+            o = kernels.paged_chunk_flash_attention(
+                d_q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
+                case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
+            h_out.copy_(o, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_e2e = max(3, min(args.steps, 20))
+        x0.record(stream)
+        for _ in range(n_e2e):
+            e2e_step()
+        x1.record(stream)
+        barrier()
+        ms_e2e = x0.elapsed_time(x1) / n_e2e
+        if sampler:
+            sampler.__exit__()
+        kernels.check_status(local_rank)
+
+    times = torch.tensor([ms_step, ms_e2e, ms_kernel], dtype=torch.float64, device=dev)
+    tot = torch.tensor([float(flops)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+    ms_step, ms_e2e, ms_kernel = times.tolist()
+    if rank == 0:
+        peak_file = ROOT / "MEASURED_PEAKS.json"
+        peak, kind = 1590.0, "fallback"
+        if peak_file.exists():
+            peak, kind = float(json.loads(peak_file.read_text())["bf16_tflops"]), "measured (burst)"
+        achieved = flops / (ms_kernel * 1e-3) / 1e12
+        line = {
+            "metric": "paged_prefill_tensor_throughput", "value": float(tot.item()) / (ms_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16", "data": "synthetic",
+            "config": {"workload": cfg_full.name, "batch": cfg_full.batch, "q_heads": cfg_full.q_heads,
+                       "kv_heads": cfg_full.kv_heads, "head_dim": 128, "page_size": 16,
+                       "prompt_lengths": f"uniform[{cfg_full.prompt_lo},{cfg_full.prompt_hi}]",
+                       "shared_prefix_pages": "0-50% of each prompt", "total_query_tokens": int(case.q_lens.sum()),
+                       "step": "kv_append(suffix tokens) + paged causal prefill",
+                       "l2": "L2 flushed by the step itself: q + out + new K/V (>200 MB) stream through every step"},
+            "flops_per_step": float(tot.item()),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "peak_source": f"of {kind}",
+                         "kernel": "paged_prefill_kernel", "us_per_launch": ms_kernel * 1e3, "traffic": None},
+            "e2e": {"value": float(tot.item()) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": (h_q.numel() + h_kv.numel()) * 2 * world,
+                    "d2h_bytes_per_step": h_out.numel() * 2 * world},
+            "gpu_launches": 2 * args.steps,
+            "clocks": sampler.summary() if sampler else None,
+        }
+        print(json.dumps(line))
+    if sampler:
+        sampler.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def main():
@@ -412,7 +548,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
-    if args.impl == "reference":
+    if isinstance(cfg, W.PrefillConfig):
+        if args.impl == "reference":
+            raise SystemExit("--impl reference times the decode workloads; see tests for the prefill oracle")
+        run_prefill(args, cfg)
+    elif args.impl == "reference":
         run_reference(args, cfg)
     else:
         run_b200(args, cfg)
