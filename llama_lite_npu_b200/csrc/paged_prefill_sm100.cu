@@ -6,22 +6,31 @@
 // (lite_llama/kernels/flashattention2_nopad.py:171-221): query row i of request r sits at
 // logical position ctx_r + i and attends to keys 0 .. ctx_r + i of that request.
 //
-// One CTA = one (request, 128-row query tile, query head).  Six warps:
-//   warp 4  producer : TMA (cp.async.bulk.tensor) of the Q tile once, then of the K and V pages of
-//                      each 64-key tile into a 2-stage ring; pages come through the block/token
-//                      table, each page of one head is two 16-row x 128-byte swizzled boxes;
-//   warp 5  MMA      : one lane issues tcgen05.mma: S = Q K^T (M128 N64 K16 x 8) into TMEM, and,
-//                      once the softmax warps have published P, O += P V (M128 N128 K16 x 4) into
-//                      a second TMEM region; tcgen05.commit signals mbarriers;
-//   warps 0-3 softmax: thread i owns query row i = TMEM lane i: tcgen05.ld of its S row, causal
-//                      mask, online softmax in the log2 domain (exp2), P rounded to fp16 and
-//                      written to shared memory in the UMMA K-major 128-byte-swizzled layout; O
-//                      accumulates in TMEM and is rescaled only when the row maximum has grown
-//                      by more than a factor 2^8 since the last rescale.
-// S for tile j+1 is issued as soon as the softmax warps have read S_j, so the tensor core works
-// while they exponentiate; two CTAs per SM (112 KB of shared memory, 256 TMEM columns each)
-// interleave their phases.  Operands are fp16, accumulation fp32, P is rounded to fp16 before
-// P V as in the reference (:166, :220), output fp16.  Tensor-bound:
+// One CTA = one (request, 128-row query tile, PAIR of query heads of one GQA group): the two
+// heads are two 128 x 128 query tiles with identical causal structure that share every K/V tile,
+// so K/V cross L2 -> shared memory once for both and the tensor core always has the other tile's
+// MMAs to run while one tile is in its softmax.  Ten warps, one CTA per SM:
+//   warp 8  producer : TMA (cp.async.bulk.tensor) of both Q tiles once, then of the K and V pages
+//                      of each 128-key tile into a 3-slot ring of 32 KB slots in which K and V
+//                      tiles alternate (K_0 V_0 K_1 V_1 ...); pages come through the block/token
+//                      table (entries fetched two tiles ahead), each page of one head is two
+//                      16-row x 128-byte swizzled boxes, one per lane;
+//   warp 9  MMA      : one lane issues tcgen05.mma.cta_group::1.kind::f16, always as M128 N128 K16
+//                      (the per-instruction cost of tcgen05.mma is nearly flat in N, so small-N
+//                      instructions waste the tensor pipe): S_g = Q_g K^T (8 instructions) into
+//                      TMEM and, once softmax group g has published P_g, O_g += P_g V (8
+//                      instructions) followed at once by that tile's next S; descriptors are built
+//                      once and only their address field advances; tcgen05.commit signals mbarriers;
+//   warps 0-3 / 4-7  : softmax group 0 / 1: thread i owns query row i = TMEM lane i of its tile:
+//                      tcgen05.ld of its S row in two 64-column halves, causal mask on diagonal
+//                      tiles only, online softmax in the log2 domain (3-input max, packed f32x2
+//                      FFMA/ADD, exp2), P rounded to fp16 and written to shared memory in the UMMA
+//                      K-major 128-byte-swizzled layout; O accumulates in TMEM and is rescaled only
+//                      when the row maximum has grown by more than a factor 2^8 since the last
+//                      rescale.
+// TMEM: 512 columns (S_0, S_1, O_0, O_1: 128 each).  Shared memory: 2 x 32 KB Q, 2 x 32 KB P,
+// 3 x 32 KB K/V ring.  Operands are fp16, accumulation fp32, P is rounded to fp16 before P V as
+// in the reference (:166, :220), output fp16.  Tensor-bound:
 // flops = 4 * 128 * sum over (query, visible key) pairs, per query head.
 //
 // Every wait is an mbarrier try-wait bounded by ~2 s of %globaltimer; a wait that runs out sets
@@ -36,22 +45,24 @@ namespace {
 
 constexpr int kD = 128;
 constexpr int kPS = 16;
-constexpr int kBM = 128;             // query rows per CTA
-constexpr int kBN = 64;              // keys per pipeline tile
+constexpr int kBM = 128;             // query rows per tile
+constexpr int kBN = 128;             // keys per pipeline tile
 constexpr int kTilePages = kBN / kPS;
-constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 4;
-constexpr int kProducerWarp = 4;
-constexpr int kMmaWarp = 5;
-constexpr int kThreads = 6 * 32;
+constexpr int kSlots = 3;            // 32 KB ring slots shared by K and V tiles
+constexpr int kGroups = 2;           // query tiles (heads) per CTA
+constexpr int kGroupWarps = 4;       // softmax warps per tile
+constexpr int kProducerWarp = kGroups * kGroupWarps;
+constexpr int kMmaWarp = kProducerWarp + 1;
+constexpr int kThreads = (kMmaWarp + 1) * 32;
 constexpr int kQBytes = kBM * kD * 2;          // 32 KB: [2 d-chunks][128 rows][128 B]
-constexpr int kKBytes = kBN * kD * 2;          // 16 KB: [2 d-chunks][64 keys][128 B]
-constexpr int kVBytes = kKBytes;
-constexpr int kPBytes = kBM * kBN * 2;         // 16 KB: [128 rows][128 B]
+constexpr int kTileBytes = kBN * kD * 2;       // 32 KB: K or V tile, [2 d-chunks][128 keys][128 B]
+constexpr int kPBytes = kBM * kBN * 2;         // 32 KB: [2 key-chunks][128 rows][128 B]
 constexpr int kHalfPage = kPS * 128;           // one TMA box: 16 rows x 128 B
-constexpr int kTmemCols = 256;                 // S at column 0 (64 used), O at column 128
-constexpr int kTmemPV = 128;
-constexpr int kSmemBytes = kQBytes + kStages * (kKBytes + kVBytes) + kPBytes + 128;
+constexpr int kTmemCols = 512;
+constexpr int kTmemS = 0;                      // S_0 at 0, S_1 at 128
+constexpr int kTmemO = 256;                    // O_0 at 256, O_1 at 384
+constexpr int kBarBytes = 256;
+constexpr int kSmemBytes = kGroups * (kQBytes + kPBytes) + kSlots * kTileBytes + kBarBytes;
 
 // tcgen05 instruction descriptor, kind::f16: fp16 A/B, fp32 accumulate.
 //   bits [4,6) D format (1 = f32), [7,10) A format (0 = f16), [10,13) B format (0 = f16),
@@ -125,6 +136,37 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
+// Packed fp32 pairs (sm_100 f32x2 arithmetic) and the 3-input maximum.
+__device__ __forceinline__ uint64_t pack_u32x2(uint32_t lo, uint32_t hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  return pack_u32x2(__float_as_uint(lo), __float_as_uint(hi));
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& lo, float& hi) {
+  uint32_t a, b;
+  asm("mov.b64 {%0, %1}, %2;\n" : "=r"(a), "=r"(b) : "l"(v));
+  lo = __uint_as_float(a);
+  hi = __uint_as_float(b);
+}
+__device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 struct PrefillParams {
   const int32_t* table;
   int64_t table_row_stride;
@@ -144,7 +186,7 @@ struct PrefillParams {
   int tiles_m;
 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, 1)
 paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
                      const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -152,8 +194,12 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const int lane = tid & 31;
   const int warp = tid >> 5;
 
-  // ---- which tile is this? (heavy query tiles first) -----------------------------------------
-  const int head = blockIdx.x;
+  // ---- which work item is this? (heavy query tiles first) ------------------------------------
+  const int pairs_per_group = (p.group + 1) / 2;
+  const int kv_head = static_cast<int>(blockIdx.x) / pairs_per_group;
+  const int pair = static_cast<int>(blockIdx.x) - kv_head * pairs_per_group;
+  const int head0 = kv_head * p.group + 2 * pair;          // query head of tile 0; tile 1 is head0 + 1
+  const bool active1 = (2 * pair + 1) < p.group;            // an odd group leaves its last head alone
   const int mt = p.tiles_m - 1 - static_cast<int>(blockIdx.y);
   const int b = blockIdx.z;
   int64_t q_len = load_len(p.q_lens, p.lens_i64, b);
@@ -173,24 +219,21 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const int64_t kv_len = ctx + row0 + rows;               // keys visible to the tile's last row
   const int n_tiles = static_cast<int>((kv_len + kBN - 1) / kBN);
   const int64_t n_pages = (kv_len + kPS - 1) / kPS;
-  const int kv_head = head / p.group;
   const int table_row = p.req_ids ? __ldg(p.req_ids + b) : b;
 
   // ---- shared memory carve-up -----------------------------------------------------------------
-  const uint32_t sm_q = smem_u32(smem);
-  const uint32_t sm_k = sm_q + kQBytes;                     // [stage][16 KB]
-  const uint32_t sm_v = sm_k + kStages * kKBytes;           // [stage][16 KB]
-  const uint32_t sm_p = sm_v + kStages * kVBytes;
-  const uint32_t sm_bar = sm_p + kPBytes;
-  const uint32_t bar_q = sm_bar;
-  const uint32_t bar_kfull = sm_bar + 8;                    // [2]
-  const uint32_t bar_vfull = sm_bar + 24;                   // [2]
-  const uint32_t bar_kvempty = sm_bar + 40;                 // [2]
-  const uint32_t bar_sfull = sm_bar + 56;
-  const uint32_t bar_sfree = sm_bar + 64;
-  const uint32_t bar_pfull = sm_bar + 72;
-  const uint32_t bar_pvfull = sm_bar + 80;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (sm_bar - sm_q) + 96);
+  const uint32_t sm_q = smem_u32(smem);                     // [group][32 KB]
+  const uint32_t sm_p = sm_q + kGroups * kQBytes;           // [group][32 KB]
+  const uint32_t sm_ring = sm_p + kGroups * kPBytes;        // [kSlots][32 KB]: K_0 V_0 K_1 V_1 ...
+  const uint32_t sm_bar = sm_ring + kSlots * kTileBytes;
+  const uint32_t bar_q = sm_bar;                            // 1
+  const uint32_t bar_full = sm_bar + 8;                     // [kSlots]  TMA bytes landed
+  const uint32_t bar_empty = bar_full + 8 * kSlots;         // [kSlots]  MMAs that read the slot completed
+  const uint32_t bar_sfull = bar_empty + 8 * kSlots;        // [kGroups] S_g of a tile is in TMEM
+  const uint32_t bar_pfull = bar_sfull + 8 * kGroups;       // [kGroups] P_g of a tile is in shared memory
+  const uint32_t bar_pvfull = bar_pfull + 8 * kGroups;      // [kGroups] O_g += P_g V of a tile completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_pvfull + 8 * kGroups - sm_q));
+  static_assert(8 + 2 * 8 * kSlots + 3 * 8 * kGroups + 8 <= kBarBytes, "barrier area too small");
   if ((sm_q & 1023u) != 0) {  // swizzled boxes and UMMA descriptors assume 1024-byte alignment
     set_status(p.status, B200KV_DEV_BAD_PAGE);
     return;
@@ -198,15 +241,15 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
-    for (int i = 0; i < kStages; ++i) {
-      mbar_init(bar_kfull + 8 * i, 1);
-      mbar_init(bar_vfull + 8 * i, 1);
-      mbar_init(bar_kvempty + 8 * i, 1);
+    for (int i = 0; i < kSlots; ++i) {
+      mbar_init(bar_full + 8 * i, 1);
+      mbar_init(bar_empty + 8 * i, 1);
     }
-    mbar_init(bar_sfull, 1);
-    mbar_init(bar_sfree, kSoftmaxWarps * 32);
-    mbar_init(bar_pfull, kSoftmaxWarps * 32);
-    mbar_init(bar_pvfull, 1);
+    for (int g = 0; g < kGroups; ++g) {
+      mbar_init(bar_sfull + 8 * g, 1);
+      mbar_init(bar_pfull + 8 * g, kGroupWarps * 32);
+      mbar_init(bar_pvfull + 8 * g, 1);
+    }
     fence_barrier_init();
   }
   if (warp == kMmaWarp) {  // TMEM allocation is a warp-wide operation
@@ -225,92 +268,135 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
 
   if (warp == kProducerWarp) {
     // ============================== TMA producer ============================================
-    const uint64_t policy_kv = l2_evict_first_policy();
+    // Ring items alternate K_0, V_0, K_1, V_1, ...; item n lives in slot n % kSlots.  A K or V
+    // tile is 8 pages x 2 head_dim halves = 16 boxes, one per lane 0..15.
+    const uint64_t policy = l2_evict_first_policy();
     if (lane == 0) {
       prefetch_tensormap(&qmap);
       prefetch_tensormap(&kmap);
       prefetch_tensormap(&vmap);
-      mbar_arrive_expect_tx(bar_q, kQBytes);
+      mbar_arrive_expect_tx(bar_q, (active1 ? 2 : 1) * kQBytes);
       // Rows past this request's q_len are the next request's rows (or zero fill past the end);
       // their results are never stored.
-      tma_load_3d(sm_q, &qmap, bar_q, 0, head, static_cast<int>(q_tok0), policy_kv);
-      tma_load_3d(sm_q + kQBytes / 2, &qmap, bar_q, 64, head, static_cast<int>(q_tok0), policy_kv);
+      const int qt = static_cast<int>(q_tok0);
+      tma_load_3d(sm_q, &qmap, bar_q, 0, head0, qt, policy);
+      tma_load_3d(sm_q + kQBytes / 2, &qmap, bar_q, 64, head0, qt, policy);
+      if (active1) {
+        tma_load_3d(sm_q + kQBytes, &qmap, bar_q, 0, head0 + 1, qt, policy);
+        tma_load_3d(sm_q + kQBytes + kQBytes / 2, &qmap, bar_q, 64, head0 + 1, qt, policy);
+      }
     }
-    const int my_page = lane >> 2;   // lanes 0..15: page of the tile
-    const int my_part = lane & 3;    // K low, K high, V low, V high half of head_dim
-    const bool is_v = (my_part & 2) != 0;
+    const int my_page = lane >> 1;   // lanes 0..15: page of the tile
+    const int my_half = lane & 1;    // low / high half of head_dim
     const int32_t* trow = p.table + static_cast<int64_t>(table_row) * p.table_row_stride;
     const int64_t dense0 = static_cast<int64_t>(__ldg(p.q_start + b));
-    for (int j = 0; j < n_tiles; ++j) {
-      const int st = j % kStages;
-      if (j >= kStages && !mbar_wait_bounded(bar_kvempty + 8 * st, ((j / kStages) - 1) & 1)) {
-        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-        break;
-      }
+    // Raw table entry of this lane's page of a tile (0 when the page does not exist).
+    auto fetch_id = [&](int j) -> int32_t {
+      const int64_t lp = static_cast<int64_t>(j) * kTilePages + my_page;
+      if (lane >= 16 || j >= n_tiles || lp >= n_pages || p.table_kind == B200KV_TABLE_DENSE) return 0;
+      return __ldg(trow + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
+    };
+    int32_t id_cur = fetch_id(0);
+    int32_t id_next = fetch_id(1);
+    bool ok = true;
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      const int32_t id_after = fetch_id(j + 2);   // in flight while this tile is issued
       const int64_t page0 = static_cast<int64_t>(j) * kTilePages;
       const int np = static_cast<int>(n_pages - page0 < kTilePages ? n_pages - page0 : kTilePages);
-      if (lane == 0) {
-        mbar_arrive_expect_tx(bar_kfull + 8 * st, np * 2 * kHalfPage);
-        mbar_arrive_expect_tx(bar_vfull + 8 * st, np * 2 * kHalfPage);
+      const int64_t lp = page0 + my_page;
+      int64_t slot;
+      if (p.table_kind == B200KV_TABLE_BLOCK) slot = static_cast<int64_t>(id_cur) * kPS;
+      else if (p.table_kind == B200KV_TABLE_TOKEN) slot = static_cast<int64_t>(id_cur);
+      else slot = dense0 + lp * kPS;   // dense packed K/V: token t of the request at q_start + t
+      if (lane < 2 * np && (slot < 0 || slot >= p.pool_tokens)) {
+        set_status(p.status, B200KV_DEV_BAD_PAGE);
+        slot = 0;  // never dereference a bad entry: report it and read page 0 instead
       }
-      __syncwarp();
-      if (lane < 4 * np) {
-        const int64_t lp = page0 + my_page;
-        int64_t slot;
-        if (p.table_kind == B200KV_TABLE_BLOCK) slot = static_cast<int64_t>(__ldg(trow + lp)) * kPS;
-        else if (p.table_kind == B200KV_TABLE_TOKEN) slot = static_cast<int64_t>(__ldg(trow + lp * kPS));
-        else slot = dense0 + lp * kPS;   // dense packed K/V: token t of the request at q_start + t
-        if (slot < 0 || slot >= p.pool_tokens) {
-          set_status(p.status, B200KV_DEV_BAD_PAGE);
-          slot = 0;  // never dereference a bad entry: report it and read page 0 instead
+      const uint32_t dst_off = my_half * (kTileBytes / 2) + my_page * kHalfPage;
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {               // item 2j = K_j, item 2j+1 = V_j
+        const int item = 2 * j + kv;
+        const int sl = item % kSlots;
+        if (item >= kSlots && !mbar_wait_bounded(bar_empty + 8 * sl, ((item / kSlots) - 1) & 1)) {
+          set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+          ok = false;
+          break;
         }
-        const uint32_t dst = (is_v ? sm_v + st * kVBytes : sm_k + st * kKBytes) +
-                             (my_part & 1) * (kKBytes / 2) + my_page * kHalfPage;
-        tma_load_3d(dst, is_v ? &vmap : &kmap, (is_v ? bar_vfull : bar_kfull) + 8 * st,
-                    (my_part & 1) * 64, kv_head, static_cast<int>(slot), policy_kv);
+        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * sl, np * 2 * kHalfPage);
+        __syncwarp();
+        if (lane < 2 * np)
+          tma_load_3d(sm_ring + sl * kTileBytes + dst_off, kv ? &vmap : &kmap, bar_full + 8 * sl, my_half * 64,
+                      kv_head, static_cast<int>(slot), policy);
       }
+      id_cur = id_next;
+      id_next = id_after;
     }
   } else if (warp == kMmaWarp) {
     // ============================== MMA issuer ==============================================
     if (lane == 0) {
       bool ok = mbar_wait_bounded(bar_q, 0);
-      const uint32_t tmem_s = tmem_base;
-      const uint32_t tmem_pv = tmem_base + kTmemPV;
-      auto issue_s = [&](int j) {
-        const int st = j % kStages;
-        if (!mbar_wait_bounded(bar_kfull + 8 * st, (j / kStages) & 1)) return false;
-        if (j > 0 && !mbar_wait_bounded(bar_sfree, (j - 1) & 1)) return false;
+      // Descriptors are built once; per instruction only the 14-bit start-address field (bytes
+      // >> 4, shared-memory addresses fit without carry) is advanced by a compile-time constant.
+      // K is the K-major B operand of S; V is the MN-major B operand of P V: 64 head_dim values
+      // contiguous (128 B), the next 64 at +16 KB (LBO), 8-key groups 1024 B apart (SBO), a K step
+      // of 16 keys advances 2048 B.
+      const uint64_t dq0 = smem_desc(sm_q, 16, 1024), dq1 = smem_desc(sm_q + kQBytes, 16, 1024);
+      const uint64_t dp0 = smem_desc(sm_p, 16, 1024), dp1 = smem_desc(sm_p + kPBytes, 16, 1024);
+      const uint64_t dk_base = smem_desc(sm_ring, 16, 1024);
+      const uint64_t dv_base = smem_desc(sm_ring, kTileBytes / 2, 1024);
+      constexpr uint64_t kSlotStep = kTileBytes >> 4;
+      constexpr uint64_t kChunkStep = (kTileBytes / 2) >> 4;   // second 64-wide chunk of an operand tile
+
+      auto issue_s = [&](int g, int j) {            // S_g = Q_g K_j^T : 8 x (M128 N128 K16)
+        const uint64_t kd = dk_base + static_cast<uint64_t>((2 * j) % kSlots) * kSlotStep;
+        const uint64_t qd = g ? dq1 : dq0;
+        const uint32_t d_s = tmem_base + kTmemS + g * kBN;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kD / 16; ++ks) {
-          const uint64_t a = smem_desc(sm_q + (ks >> 2) * (kQBytes / 2) + (ks & 3) * 32, 16, 1024);
-          const uint64_t bd =
-              smem_desc(sm_k + st * kKBytes + (ks >> 2) * (kKBytes / 2) + (ks & 3) * 32, 16, 1024);
-          umma_f16(tmem_s, a, bd, kIdescS, ks > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>((ks >> 2) * kChunkStep + (ks & 3) * 2);
+          if (ks == 0) umma_f16(d_s, qd + off, kd + off, kIdescS, 0u);
+          else umma_f16(d_s, qd + off, kd + off, kIdescS, 1u);
         }
-        umma_commit(bar_sfull);
-        return true;
+        umma_commit(bar_sfull + 8 * g);
       };
-      if (ok) ok = issue_s(0);
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        const int st = j % kStages;
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);   // S of the next tile overlaps this tile's softmax
-        if (!ok) break;
-        if (!mbar_wait_bounded(bar_pfull, j & 1) || !mbar_wait_bounded(bar_vfull + 8 * st, (j / kStages) & 1)) {
-          ok = false;
-          break;
-        }
+      auto issue_pv = [&](int g, int j) {           // O_g += P_g V_j : 8 x (M128 N128 K16)
+        const uint64_t vd = dv_base + static_cast<uint64_t>((2 * j + 1) % kSlots) * kSlotStep;
+        const uint64_t pd = g ? dp1 : dp0;
+        const uint32_t d_o = tmem_base + kTmemO + g * kD;
         tc_fence_after();
 #pragma unroll
         for (int ks = 0; ks < kBN / 16; ++ks) {
-          const uint64_t a = smem_desc(sm_p + ks * 32, 16, 1024);
-          // V tile is MN-major for B: 64 head_dim values contiguous (128 B), next 64 at +8 KB (LBO),
-          // 8-key groups 1024 B apart (SBO); a K step of 16 keys advances 16 rows = 2048 B.
-          const uint64_t bd = smem_desc(sm_v + st * kVBytes + ks * 2048, kVBytes / 2, 1024);
-          umma_f16(tmem_pv, a, bd, kIdescPV, (j > 0 || ks > 0) ? 1u : 0u);
+          const uint64_t a = pd + static_cast<uint64_t>((ks >> 2) * kChunkStep + (ks & 3) * 2);
+          const uint64_t bd = vd + static_cast<uint64_t>(ks * (2048 >> 4));
+          if (ks == 0) umma_f16(d_o, a, bd, kIdescPV, j > 0 ? 1u : 0u);
+          else umma_f16(d_o, a, bd, kIdescPV, 1u);
         }
-        umma_commit(bar_pvfull);
-        umma_commit(bar_kvempty + 8 * st);
+        umma_commit(bar_pvfull + 8 * g);
+      };
+      const int ng = active1 ? 2 : 1;
+      // Tensor-core order: S0_0 S1_0 | PV0_0 S0_1 | PV1_0 S1_1 | PV0_1 S0_2 | ...  A tile's next S is
+      // issued right behind its P V, so one tile is in its softmax while the other's MMAs run.
+      if (ok) ok = mbar_wait_bounded(bar_full + 8 * 0, 0);
+      if (ok) {
+        for (int g = 0; g < ng; ++g) issue_s(g, 0);
+        umma_commit(bar_empty + 8 * 0);                     // K_0: both S issued
+      }
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        const int kslot_next = (2 * j + 2) % kSlots, vslot = (2 * j + 1) % kSlots;
+        const bool more = j + 1 < n_tiles;
+        for (int g = 0; g < ng; ++g) {
+          if (!mbar_wait_bounded(bar_pfull + 8 * g, j & 1)) { ok = false; break; }
+          if (g == 0 && !mbar_wait_bounded(bar_full + 8 * vslot, ((2 * j + 1) / kSlots) & 1)) { ok = false; break; }
+          issue_pv(g, j);
+          if (more) {
+            if (g == 0 && !mbar_wait_bounded(bar_full + 8 * kslot_next, ((2 * j + 2) / kSlots) & 1)) { ok = false; break; }
+            issue_s(g, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(bar_empty + 8 * vslot);                 // V_j: both P V issued
+        if (more) umma_commit(bar_empty + 8 * kslot_next);  // K_{j+1}: both S issued
       }
       if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
     }
@@ -319,34 +405,53 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
     // O accumulates in TMEM.  The running maximum used to scale P and O (m_used) is only moved
     // when the true row maximum has grown by more than 8 (a factor 256, harmless for fp16 P and
     // fp32 accumulation): then O and l are rescaled once; otherwise a tile costs no pass over O.
-    const int row = tid;                                   // query row of the tile = TMEM lane
-    const uint32_t t_lane = static_cast<uint32_t>(warp * 32) << 16;
-    const uint32_t tmem_o = tmem_base + t_lane + kTmemPV;
+    // A 128-key S row is handled as two 64-column halves to stay within the register budget: both
+    // halves are read for the maximum, the second is exponentiated from registers, the first is
+    // re-read from TMEM (cheap) and exponentiated last.
+    const int g = warp / kGroupWarps;                      // which query tile (head) of the pair
+    const int gtid = tid - g * kGroupWarps * 32;
+    const int row = gtid;                                  // query row of the tile = TMEM lane
+    const bool active = (g == 0) || active1;
+    const uint32_t t_lane = static_cast<uint32_t>((warp % kGroupWarps) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + t_lane + kTmemS + g * kBN;
+    const uint32_t tmem_o = tmem_base + t_lane + kTmemO + g * kD;
+    const uint32_t my_p = sm_p + g * kPBytes;
+    const uint32_t b_sfull = bar_sfull + 8 * g, b_pfull = bar_pfull + 8 * g, b_pvfull = bar_pvfull + 8 * g;
     const int64_t q_pos = ctx + row0 + row;                // logical position of this query row
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait_bounded(bar_sfull, j & 1)) { ok = false; break; }
+    for (int j = 0; active && j < n_tiles; ++j) {
+      if (!mbar_wait_bounded(b_sfull, j & 1)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sr[2][32];
-      tmem_ld32(tmem_base + t_lane + 0, sr[0]);
-      tmem_ld32(tmem_base + t_lane + 32, sr[1]);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(bar_sfree);                              // S_j is in registers: S_{j+1} may start
       const int64_t key0 = static_cast<int64_t>(j) * kBN;
-      const bool need_mask = key0 + kBN - 1 > ctx + row0;  // tile reaches past the first row's diagonal
-      float sv[kBN];
-      float mx = -INFINITY;
+      // Only tiles that reach past the first row's diagonal need the causal mask (warp-uniform).
+      const bool need_mask = key0 + kBN - 1 > ctx + row0;
+      const int lim = static_cast<int>(q_pos - key0 < kBN ? q_pos - key0 : kBN);  // keys c <= lim visible
+      uint32_t sr[2][32];
+      auto load_half = [&](int h) {
+        tmem_ld32(tmem_s + h * 64 + 0, sr[0]);
+        tmem_ld32(tmem_s + h * 64 + 32, sr[1]);
+        tmem_ld_wait();
+        if (need_mask) {
 #pragma unroll
-      for (int c = 0; c < kBN; ++c) {
-        float sc = __uint_as_float(sr[c >> 5][c & 31]) * p.scale_log2;
-        if (need_mask && key0 + c > q_pos) sc = -INFINITY;
-        sv[c] = sc;
-        mx = fmaxf(mx, sc);
-      }
-      // P_{j-1} and O are free once PV_{j-1} has completed.
-      if (j > 0 && !mbar_wait_bounded(bar_pvfull, (j - 1) & 1)) { ok = false; break; }
+          for (int c = 0; c < 64; ++c)
+            if (h * 64 + c > lim) sr[c >> 5][c & 31] = 0xff800000u;   // -inf
+        }
+      };
+      auto half_max = [&](float mx) {   // raw scores (the scale is positive), two per instruction
+#pragma unroll
+        for (int c = 0; c < 64; c += 2)
+          mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+        return mx;
+      };
+      float mx = -INFINITY;
+      load_half(0);
+      mx = half_max(mx);
+      load_half(1);
+      mx = half_max(mx) * p.scale_log2;
+      // P_g and O_g are free once the P V MMAs of tile j-1 have completed (they were issued
+      // before this tile's S, so this wait is normally already satisfied).
+      if (j > 0 && !mbar_wait_bounded(b_pvfull, (j - 1) & 1)) { ok = false; break; }
       const bool grow = mx > m_used + 8.f;                 // also true on the first tile (m_used = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_used;
@@ -355,7 +460,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         m_used = m_new;
         if (j > 0) {                                       // rescale this warp's 32 rows of O
           tc_fence_after();
-#pragma unroll
+#pragma unroll 1
           for (int q4 = 0; q4 < kD / 32; ++q4) {
             uint32_t ov[32];
             tmem_ld32(tmem_o + q4 * 32, ov);
@@ -368,53 +473,75 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
           tc_fence_before();
         }
       }
-      const float msub = (m_used == -INFINITY) ? 0.f : m_used;
-      float rs = 0.f;
-      // P row -> shared memory, UMMA K-major layout with the 128-byte swizzle: row r at r*128 B,
-      // its eight 16-byte chunks XOR-ed with r % 8.
-      const uint32_t prow = sm_p + row * 128;
+      // p = 2^(s * scale - m): one packed FFMA per two elements, then exp2, packed row sums.
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const uint64_t negm2 = pack_f32x2(neg_m, neg_m);
+      uint64_t rs2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
+      // P row -> shared memory, UMMA K-major layout with the 128-byte swizzle: 64-key chunk h is a
+      // [128 rows][128 B] block, row r at r*128 B, its eight 16-byte pieces XOR-ed with r % 8.
+      auto exp_store_half = [&](int h) {
+        const uint32_t prow = my_p + h * (kPBytes / 2) + row * 128;
 #pragma unroll
-      for (int ch = 0; ch < kBN / 8; ++ch) {
-        uint32_t pk[4];
+        for (int ch = 0; ch < 8; ++ch) {
+          uint32_t pk[4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(sv[ch * 8 + 2 * e] - msub);
-          const float p1 = fast_exp2(sv[ch * 8 + 2 * e + 1] - msub);
-          rs += p0 + p1;
-          pk[e] = pack_half2(p0, p1);
+          for (int e = 0; e < 4; ++e) {
+            const int c = ch * 8 + 2 * e;
+            const uint64_t x2 =
+                fma_f32x2(pack_u32x2(sr[c >> 5][c & 31], sr[(c + 1) >> 5][(c + 1) & 31]), scale2, negm2);
+            float x0, x1;
+            unpack_f32x2(x2, x0, x1);
+            const float p0 = fast_exp2(x0);
+            const float p1 = fast_exp2(x1);
+            rs2[e & 1] = add_f32x2(rs2[e & 1], pack_f32x2(p0, p1));
+            pk[e] = pack_half2(p0, p1);
+          }
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
+                       "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+                       : "memory");
         }
-        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
-                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                     : "memory");
+      };
+      exp_store_half(1);        // still in registers
+      load_half(0);
+      tc_fence_before();
+      exp_store_half(0);
+      {
+        float a0, a1, b0, b1;
+        unpack_f32x2(rs2[0], a0, a1);
+        unpack_f32x2(rs2[1], b0, b1);
+        l_run += (a0 + a1) + (b0 + b1);
       }
-      l_run += rs;
-      if (j == n_tiles - 1) {
+      if (g == 0 && j == n_tiles - 1) {
         // Keys past kv_len in the last tile were either not loaded or lie in never-written pool
-        // slots; their P is 0 but 0 * NaN would still poison the row, so zero those V rows.
-        const int st = j % kStages;
+        // slots; their P is 0 but 0 * NaN would still poison the row, so zero those V rows.  Group
+        // 0 does it before publishing P_0; the MMA warp waits for P_0 before issuing either
+        // tile's P V, so both tiles read the cleaned V.
+        const int item = 2 * j + 1;
+        const int sl = item % kSlots;
         const int valid = static_cast<int>(kv_len - key0);
         if (valid < kBN) {
-          if (!mbar_wait_bounded(bar_vfull + 8 * st, (j / kStages) & 1)) { ok = false; break; }
-          for (int i = tid; i < (kBN - valid) * 16; i += kSoftmaxWarps * 32) {
+          if (!mbar_wait_bounded(bar_full + 8 * sl, (item / kSlots) & 1)) { ok = false; break; }
+          for (int i = gtid; i < (kBN - valid) * 16; i += kGroupWarps * 32) {
             const int r = valid + (i >> 4);
             const int c = i & 15;
             asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};\n" ::"r"(
-                             sm_v + st * kVBytes + (c >> 3) * (kVBytes / 2) + r * 128 + ((c & 7) << 4)),
+                             sm_ring + sl * kTileBytes + (c >> 3) * (kTileBytes / 2) + r * 128 + ((c & 7) << 4)),
                          "r"(0)
                          : "memory");
           }
         }
       }
       fence_proxy_async_smem();                            // P (and V fix-ups) visible to the tensor core
-      mbar_arrive(bar_pfull);
+      mbar_arrive(b_pfull);
     }
-    if (ok && !mbar_wait_bounded(bar_pvfull, (n_tiles - 1) & 1)) ok = false;
+    if (active && ok && !mbar_wait_bounded(b_pvfull, (n_tiles - 1) & 1)) ok = false;
     if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-    if (ok) {
+    if (active && ok) {
       tc_fence_after();
       const float inv = 1.f / l_run;
-      __half* op = p.out + (q_tok0 + row) * p.out_stride_t + static_cast<int64_t>(head) * p.out_stride_h;
-#pragma unroll
+      __half* op = p.out + (q_tok0 + row) * p.out_stride_t + static_cast<int64_t>(head0 + g) * p.out_stride_h;
+#pragma unroll 1
       for (int q4 = 0; q4 < kD / 32; ++q4) {
         uint32_t ov[32];
         tmem_ld32(tmem_o + q4 * 32, ov);                   // warp-collective: every lane takes part
@@ -517,8 +644,9 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(a.q_heads), static_cast<unsigned>(p.tiles_m),
-                     static_cast<unsigned>(a.batch));
+  // x: (KV head, pair of query heads of its group), adjacent so a group's CTAs share K/V in L2.
+  cfg.gridDim = dim3(static_cast<unsigned>(a.kv_heads * ((p.group + 1) / 2)),
+                     static_cast<unsigned>(p.tiles_m), static_cast<unsigned>(a.batch));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
