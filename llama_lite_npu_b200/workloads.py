@@ -306,3 +306,64 @@ def make_prefill_case(cfg: PrefillConfig, device="cpu", fill="hash",
         ctx_lens_t=torch.from_numpy(ctx).to(device), q_lens_t=torch.from_numpy(qn).to(device),
         q=q, new_kv=new_kv, slots=torch.from_numpy(slots).to(device), max_q_len=int(qn.max()),
     )
+
+
+# ---------------------------------------------------------------------------------------------
+# Sharding one job over the GPUs of a box (no collective: every shard is self-contained)
+# ---------------------------------------------------------------------------------------------
+def head_shard(kv_heads: int, q_heads: int, world_size: int, rank: int):
+    """(kv head slice, q head slice) owned by ``rank``: a contiguous block of KV heads with the
+    query heads of their groups, the layout a tensor-parallel attention layer uses."""
+    if kv_heads % world_size != 0:
+        raise ValueError(f"{kv_heads} KV heads do not split over {world_size} ranks")
+    per = kv_heads // world_size
+    group = q_heads // kv_heads
+    return slice(rank * per, (rank + 1) * per), slice(rank * per * group, (rank + 1) * per * group)
+
+
+def _shard_pool(pool: torch.Tensor, kv_heads: int, kv_sl: slice) -> torch.Tensor:
+    k = pool[:, :kv_heads][:, kv_sl]
+    v = pool[:, kv_heads:][:, kv_sl]
+    return torch.cat([k, v], dim=1).contiguous()
+
+
+def shard_decode_case(case: DecodeCase, world_size: int, rank: int) -> DecodeCase:
+    """KV-head shard of a decode step: same sequences, tables, lengths and slots; this rank's
+    heads of q, of the pool and of the appended rows.  Concatenating the shards' outputs along
+    the head axis gives the unsharded output."""
+    cfg = case.cfg
+    kv_sl, q_sl = head_shard(cfg.kv_heads, cfg.q_heads, world_size, rank)
+    return DecodeCase(
+        cfg=shard_kv_heads(cfg, world_size, rank), seq_lens=case.seq_lens, pages=case.pages,
+        pool=_shard_pool(case.pool, cfg.kv_heads, kv_sl), token_table=case.token_table,
+        block_table=case.block_table, seq_lens_t=case.seq_lens_t, q=case.q[:, q_sl].contiguous(),
+        new_kv=_shard_pool(case.new_kv, cfg.kv_heads, kv_sl), slots=case.slots, max_len=case.max_len,
+    )
+
+
+def shard_prefill_case(case: PrefillCase, world_size: int, rank: int) -> PrefillCase:
+    cfg = case.cfg
+    kv_sl, q_sl = head_shard(cfg.kv_heads, cfg.q_heads, world_size, rank)
+    out = PrefillCase(**{**case.__dict__})
+    out.cfg = shard_kv_heads(cfg, world_size, rank)
+    out.pool = _shard_pool(case.pool, cfg.kv_heads, kv_sl)
+    out.new_kv = _shard_pool(case.new_kv, cfg.kv_heads, kv_sl)
+    out.q = case.q[:, q_sl].contiguous()
+    return out
+
+
+def shard_decode_requests(case: DecodeCase, world_size: int, rank: int) -> DecodeCase:
+    """Request shard (used when KV heads are fewer than ranks): requests rank::world_size with all
+    heads; tables keep their page ids, so the rank needs the same pool (or its own copy of the
+    pages it references)."""
+    idx = np.arange(rank, case.cfg.batch, world_size)
+    t = torch.from_numpy(idx)
+    kwargs = dict(case.cfg.__dict__)
+    kwargs["batch"] = len(idx)
+    return DecodeCase(
+        cfg=DecodeConfig(**kwargs), seq_lens=case.seq_lens[idx], pages=[case.pages[i] for i in idx],
+        pool=case.pool, token_table=case.token_table[t].contiguous(),
+        block_table=case.block_table[t].contiguous(), seq_lens_t=case.seq_lens_t[t].contiguous(),
+        q=case.q[t].contiguous(), new_kv=case.new_kv[t].contiguous(), slots=case.slots[t].contiguous(),
+        max_len=int(case.seq_lens[idx].max()) if len(idx) else 0,
+    )

@@ -356,3 +356,76 @@ def test_prefill_c4_full_size_properties():
         c.req_ids.to(DEV), c.q_start.to(DEV), c.ctx_lens_t.to(DEV), c.q_lens_t.to(DEV), c.max_q_len,
         table_kind="block")
     assert _maxdiff(out_c, torch.full_like(out_c, 0.25)) <= 1e-3
+
+
+# ---- sharding and the remaining full-size configurations -------------------------------------
+def _decode_step_gpu(c, table_kind="block"):
+    kh = c.cfg.kv_heads
+    pool = c.pool.to(DEV)
+    kernels.update_kv_buffer(c.new_kv.to(DEV), c.slots.to(DEV), pool)
+    tbl = (c.block_table if table_kind == "block" else c.token_table).to(DEV)
+    return kernels.flash_decoding(c.q.to(DEV), pool[:, :kh], pool[:, kh:], SCALE, tbl,
+                                  c.seq_lens_t.to(DEV), c.max_len, table_kind=table_kind)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_kv_head_shards_on_gpu_reassemble(world):
+    """Each KV-head shard (what one GPU of an N-GPU box runs) through the CUDA path; the shards
+    concatenated along heads must equal the oracle of the whole job."""
+    full = W.make_decode_case(W.C1, fill="hash")       # 16 Q / 8 KV heads
+    parts = [_decode_step_gpu(W.shard_decode_case(full, world, r)).cpu() for r in range(world)]
+    got = torch.cat(parts, dim=1)
+    pool = full.pool.clone()
+    O.kv_append(full.new_kv, full.slots, pool)
+    want = O.paged_decode(full.q, pool[:, :8], pool[:, 8:], SCALE, full.token_table, full.seq_lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
+
+
+def test_request_shards_on_gpu_reassemble():
+    full = G.build_decode("decode_gqa8_small")
+    got = torch.zeros_like(full.q)
+    for r in range(2):
+        got[r::2] = _decode_step_gpu(W.shard_decode_requests(full, 2, r)).cpu()
+    pool = full.pool.clone()
+    O.kv_append(full.new_kv, full.slots, pool)
+    want = O.paged_decode(full.q, pool[:, :2], pool[:, 2:], SCALE, full.token_table, full.seq_lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
+
+
+def _check_sampled_sequences(c, out, batch_ids):
+    kh = c.cfg.kv_heads
+    for b in batch_ids:
+        L = int(c.seq_lens[b])
+        slots = c.token_table[b, :L].long()
+        k = c.k_cache[slots].cpu()
+        v = c.v_cache[slots].cpu()
+        table = torch.arange(L, dtype=torch.int32)[None]
+        want = O.paged_decode(c.q[b: b + 1].cpu(), k, v, SCALE, table, torch.tensor([L]))
+        assert _maxdiff(out[b: b + 1], want) <= ATTN_TOL, (b, L)
+
+
+def test_decode_c3_full_size():
+    """Qwen3-30B-A3B shape: batch 64, 32 Q / 4 KV heads, fixed context 2048, shuffled pages."""
+    c = W.make_decode_case(W.C3, device=DEV, fill="randn")
+    kernels.update_kv_buffer(c.new_kv, c.slots, c.pool)
+    out = kernels.flash_decoding(c.q, c.k_cache, c.v_cache, SCALE, c.token_table, c.seq_lens_t,
+                                 c.max_len)                      # the reference's token table
+    _check_sampled_sequences(c, out, (0, 21, 63))
+    assert torch.equal(c.pool[c.slots.long()], c.new_kv)
+
+
+def test_decode_c5_long_mixed_lengths():
+    """Long mixed-length stress at the C5 shape (batch 128, lengths log-uniform in [16, 32768],
+    64 Q / 8 KV heads) on a pool just large enough for the drawn lengths (the full 2^20-page pool
+    is 64 GiB; its size does not change what a kernel reads).  Checked against the oracle: every
+    sequence shorter than 300 tokens and the longest one."""
+    lens = W.draw_lengths(W.C5)
+    pages = int(np.ceil(lens / 16).sum())
+    cfg = W.DecodeConfig("c5_compact_pool", 128, 64, 8, pages + 64, 16, 32768, "loguniform", seed=1005)
+    c = W.make_decode_case(cfg, device=DEV, fill="randn", lengths=lens)
+    out = kernels.flash_decoding(c.q, c.k_cache, c.v_cache, SCALE, c.block_table, c.seq_lens_t,
+                                 c.max_len, table_kind="block")
+    ids = [int(i) for i in np.nonzero(lens < 300)[0]] + [int(np.argmax(lens))]
+    assert len(ids) > 10 and int(lens.max()) > 20000
+    _check_sampled_sequences(c, out, ids)
+    kernels.check_status(0)
