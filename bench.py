@@ -307,22 +307,32 @@ def run_b200(args, cfg_full):
         ms_kernel = timed(decode_only, n_k) / n_k
 
         # ---- e2e: operator API, host inputs in, result out, every step -----------------------
-        h_q = case.q.cpu().pin_memory()
-        h_kv = case.new_kv.cpu().pin_memory()
-        h_slots = case.slots.cpu().pin_memory()
-        h_lens = case.seq_lens_t.cpu().pin_memory()
-        h_out = torch.empty_like(h_q).pin_memory()
-        d_q, d_kv = torch.empty_like(case.q), torch.empty_like(case.new_kv)
-        d_slots, d_lens = torch.empty_like(case.slots), torch.empty_like(case.seq_lens_t)
-        h2d = sum(t.numel() * t.element_size() for t in (h_q, h_kv, h_slots, h_lens))
+        # The step's host inputs (q, the new K/V rows, slot_mapping, lengths) sit in ONE pinned
+        # staging buffer and cross PCIe in one copy; the result comes back in one copy.
+        parts = [("q", case.q), ("kv", case.new_kv), ("lens", case.seq_lens_t), ("slots", case.slots)]
+        offs, cur = {}, 0
+        for name, t in parts:
+            cur = (cur + 15) // 16 * 16
+            offs[name] = (cur, t.numel() * t.element_size())
+            cur += t.numel() * t.element_size()
+        h_in = torch.empty(cur, dtype=torch.uint8).pin_memory()
+        d_in = torch.empty(cur, dtype=torch.uint8, device=dev)
+
+        def view(buf, name, like):
+            o, n = offs[name]
+            return buf[o:o + n].view(like.dtype).view(like.shape)
+
+        for name, t in parts:
+            view(h_in, name, t).copy_(t.cpu())
+        d_q, d_kv = view(d_in, "q", case.q), view(d_in, "kv", case.new_kv)
+        d_lens, d_slots = view(d_in, "lens", case.seq_lens_t), view(d_in, "slots", case.slots)
+        h_out = torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory()
+        h2d = cur
         d2h = h_out.numel() * h_out.element_size()
 
         def e2e_step(i):
             pool = pools[i % layers]
-            d_q.copy_(h_q, non_blocking=True)
-            d_kv.copy_(h_kv, non_blocking=True)
-            d_slots.copy_(h_slots, non_blocking=True)
-            d_lens.copy_(h_lens, non_blocking=True)
+            d_in.copy_(h_in, non_blocking=True)
             kernels.update_kv_buffer(d_kv, d_slots, pool)
             o = kernels.flash_decoding(d_q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
                                        d_lens, case.max_len, table_kind="block")

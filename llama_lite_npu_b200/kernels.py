@@ -73,6 +73,27 @@ def _stream(device_index: int) -> int:
     return torch.cuda.current_stream(device_index).cuda_stream
 
 
+class _NoSwitch:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_SWITCH = _NoSwitch()
+
+
+def _on_device(device_index: int):
+    """Context that makes ``device_index`` current; free when it already is (the common case)."""
+    if torch.cuda.current_device() == device_index:
+        return _NO_SWITCH
+    return torch.cuda.device(device_index)
+
+
+_workspace_need: dict[tuple, int] = {}
+
+
 def _require(cond: bool, msg: str) -> None:
     if not cond:
         raise ValueError(msg)
@@ -97,8 +118,12 @@ def _kv_views(k_cache: torch.Tensor, v_cache: torch.Tensor):
 def decode_workspace(device_index: int, batch: int, q_heads: int, kv_heads: int, head_dim: int):
     """Per-device scratch for split-KV partials; grown on demand, never shrunk, so its
     address is stable across calls of the same or a smaller shape."""
-    with torch.cuda.device(device_index):
-        need = _lib.lib().b200kv_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim)
+    key = (device_index, batch, q_heads, kv_heads, head_dim)
+    need = _workspace_need.get(key)
+    if need is None:
+        with _on_device(device_index):
+            need = _lib.lib().b200kv_decode_workspace_bytes(batch, q_heads, kv_heads, head_dim)
+        _workspace_need[key] = need
     if need == 0:
         raise ValueError(
             "unsupported decode shape: head_dim must be 128 and q_heads/kv_heads an integer <= 16"
@@ -139,7 +164,7 @@ def update_kv_buffer(KV_Values: torch.Tensor, Select_Index: torch.Tensor, KV_Buf
              "KV_Buffer must be contiguous inside a token")
     if not Select_Index.is_contiguous():
         Select_Index = Select_Index.contiguous()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.lib().b200kv_kv_append(
             KV_Values.data_ptr(), n, KV_Values.stride(0), Select_Index.data_ptr(),
             KV_Buffer.data_ptr(), KV_Buffer.shape[0], KV_Buffer.stride(0), rows, d,
@@ -172,7 +197,7 @@ def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: tor
         return
     if not Select_Index.is_contiguous():
         Select_Index = Select_Index.contiguous()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.lib().b200kv_kv_append_split(
             xk.data_ptr(), xv.data_ptr(), n, xk.stride(0), xv.stride(0), Select_Index.data_ptr(),
             KV_Buffer.data_ptr(), KV_Buffer.shape[0], KV_Buffer.stride(0), kvh, d,
@@ -242,7 +267,7 @@ def flash_decoding(
     if batch == 0:
         return out
     ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.lib().b200kv_paged_decode(
             q.data_ptr(), q.stride(0), q.stride(1),
             k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
@@ -265,7 +290,7 @@ def _prefill_call(q, k_cache, v_cache, scale_log2, tbl_ptr, tbl_stride, kind, re
     output = torch.empty_like(q)
     if q.numel() == 0 or batch == 0:
         return output
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = _lib.lib().b200kv_paged_prefill(
             q.data_ptr(), q.stride(0), q.stride(1),
             k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
