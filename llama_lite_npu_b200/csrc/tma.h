@@ -56,11 +56,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // without such a bound.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // Fast path: a few thousand hardware-suspended tries without touching the clock (reading
+  // %globaltimer costs far more than a try, and almost every wait ends here).
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = global_timer_ns();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 32; ++i)
+    for (int i = 0; i < 256; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - t0 > kWaitLimitNs) return false;
   }
