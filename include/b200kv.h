@@ -217,6 +217,18 @@ int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h,
                          void* out, int64_t out_stride_t, int64_t out_stride_h,
                          int32_t* status, void* stream);
 
+/*
+ * Self-test of the bounded device-side wait every pipelined kernel here relies
+ * on (no counterpart in the reference).  Launches one small CTA that waits on
+ * two mbarriers for at most limit_ns (1 ns .. 1 s) each: the first receives its
+ * arrival, the second never does.  On return (after synchronising the stream)
+ * result[0] == 1 (the first wait completed), result[1] == 0 (the second gave up)
+ * and *status == B200KV_DEV_WAIT_TIMEOUT.  Nothing faults or hangs: this is how
+ * a lost copy or a missing producer surfaces in the real kernels (limit ~2 s).
+ *   result  device int32[2];  status  device int32 (zeroed by the caller) or NULL
+ */
+int b200kv_selftest_bounded_wait(uint64_t limit_ns, int32_t* result, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,7 +8,7 @@ operator in :mod:`llama_lite_npu_b200.kernels` fails with it.
 from __future__ import annotations
 
 import ctypes
-from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200kv.so"
@@ -54,6 +54,7 @@ _SIGNATURES = {
          c_void_p, c_int64, c_int64,
          c_void_p, c_void_p],
     ),
+    "b200kv_selftest_bounded_wait": (c_int, [c_uint64, c_void_p, c_void_p, c_void_p]),
     "b200kv_paged_prefill": (
         c_int,
         [c_void_p, c_int64, c_int64,

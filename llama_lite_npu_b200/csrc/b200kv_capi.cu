@@ -203,4 +203,8 @@ int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h, 
   return b200kv::paged_prefill(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_selftest_bounded_wait(uint64_t limit_ns, int32_t* result, int32_t* status, void* stream) {
+  return b200kv::wait_selftest(limit_ns, result, status, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

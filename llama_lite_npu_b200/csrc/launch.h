@@ -70,5 +70,6 @@ struct PrefillArgs {
   int32_t* status;
 };
 int paged_prefill(const PrefillArgs& a, cudaStream_t stream);
+int wait_selftest(uint64_t limit_ns, int32_t* result, int32_t* status, cudaStream_t stream);
 
 }  // namespace b200kv

@@ -5,9 +5,39 @@
 #include <cstdio>
 
 #include "b200kv.h"
+#include "common.cuh"
 #include "launch.h"
 
 namespace b200kv {
+
+namespace {
+// One CTA, 64 threads.  Barrier A gets its single arrival (the wait on it must succeed);
+// barrier B never does (the wait on it must give up after limit_ns and report it).
+__global__ void wait_selftest_kernel(uint64_t limit_ns, int32_t* result, int32_t* status) {
+  __shared__ uint64_t bars[2];
+  const uint32_t a = smem_u32(&bars[0]), b = smem_u32(&bars[1]);
+  if (threadIdx.x == 0) {
+    mbar_init(a, 1);
+    mbar_init(b, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 32) mbar_arrive(a);
+  const bool got_a = mbar_wait_limit(a, 0, limit_ns);
+  const bool got_b = mbar_wait_limit(b, 0, limit_ns);
+  if (!got_b) set_status(status, B200KV_DEV_WAIT_TIMEOUT);
+  if (threadIdx.x == 0) {
+    result[0] = got_a ? 1 : 0;
+    result[1] = got_b ? 1 : 0;
+  }
+}
+}  // namespace
+
+int wait_selftest(uint64_t limit_ns, int32_t* result, int32_t* status, cudaStream_t stream) {
+  if (!result || limit_ns == 0 || limit_ns > 1000000000ull) return B200KV_EINVAL;
+  wait_selftest_kernel<<<1, 64, 0, stream>>>(limit_ns, result, status);
+  return check_launch();
+}
 
 namespace {
 

@@ -55,6 +55,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // and the caller records B200KV_DEV_WAIT_TIMEOUT and leaves.  No wait in this library spins
 // without such a bound.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// Same wait with an explicit limit (used by the self-test with a limit of a few milliseconds).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+  const uint64_t t0 = global_timer_ns();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > limit_ns) return false;
+  }
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
   // Fast path: a few thousand hardware-suspended tries without touching the clock (reading
   // %globaltimer costs far more than a try, and almost every wait ends here).

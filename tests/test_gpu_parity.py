@@ -429,3 +429,23 @@ def test_decode_c5_long_mixed_lengths():
     assert len(ids) > 10 and int(lens.max()) > 20000
     _check_sampled_sequences(c, out, ids)
     kernels.check_status(0)
+
+
+# ---- failure detection without a fault ---------------------------------------------------------
+def test_bounded_wait_times_out_cleanly_and_context_survives(built_lib):
+    """A device-side wait that nothing satisfies must give up after its limit, report
+    WAIT_TIMEOUT through the status word, and leave the GPU usable."""
+    result = torch.full((2,), -1, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rc = built_lib.b200kv_selftest_bounded_wait(2_000_000, result.data_ptr(), status.data_ptr(),
+                                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert result.tolist() == [1, 0]
+    assert int(status.item()) == 104 and b"wait" in built_lib.b200kv_strerror(104)
+    assert built_lib.b200kv_selftest_bounded_wait(0, result.data_ptr(), None, None) == 1   # bad limit
+    # the context is intact: a real kernel still runs and is correct afterwards
+    c = G.build_decode("decode_mha")
+    got = _decode_gpu(c, "block")
+    want = O.paged_decode(c.q, c.k_cache, c.v_cache, SCALE, c.token_table, c.seq_lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
