@@ -19,14 +19,16 @@
 //     whole sequence) or an fp32 partial (normalised output + log2-domain log-sum-exp) in
 //     slot team + b of the workspace, merged afterwards by decode_combine_kernel.
 //
-// Pipeline inside a CTA (128 threads, 4 warps, 2 CTAs per SM): tiles of 64 tokens (4
-// pages; K and V rows of 256 B each) are staged through a 3-deep cp.async ring of 32 KB
-// stages that keeps running across piece boundaries (the page-table entries of a tile are
-// fetched three tiles before its copies are issued); shared-memory rows are XOR-swizzled
-// in 16-byte chunks so ldmatrix is conflict-free.  Warp w owns tokens [16w, 16w+16) of
-// every tile: S^T = K Q^T and O^T += V^T P^T run on mma.sync m16n8k16 (fp16 in, fp32
-// accumulate) with the tokens as the M rows and the G query heads as the N columns;
-// per-warp online-softmax states are merged through shared memory at the end of a piece.
+// Pipeline inside a CTA (5 warps, 2 CTAs per SM): tiles of 64 tokens (4 pages; K and V rows
+// of 256 B each) flow through a 3-deep ring of 32 KB stages that keeps running across piece
+// boundaries.  Warp 4 is the producer: it fetches page-table entries four tiles ahead, waits
+// for a stage's "empty" mbarrier, arms its "full" mbarrier with the byte count and issues the
+// tile's 16 TMA copies (cp.async.bulk.tensor, 16 rows x 128 B boxes with the 128-byte swizzle,
+// so ldmatrix is conflict-free), one per lane.  Warps 0..3 are consumers: warp w owns page w
+// (tokens [16w, 16w+16)) of every tile: S^T = K Q^T and O^T += V^T P^T run on mma.sync
+// m16n8k16 (fp16 in, fp32 accumulate) with the tokens as the M rows and the G query heads as
+// the N columns; per-warp online-softmax states are merged through shared memory at the end
+// of a piece.  No CTA-wide barrier in the steady state; every wait is time-bounded.
 // The kernel is HBM-bound: algorithmic bytes per token per KV head = 2 (K,V) * 128 * 2 B.
 #include "common.cuh"
 #include "launch.h"
@@ -427,11 +429,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     }
 
     const int wtok = t.ntok - warp * kPS;  // valid tokens of this warp's page (may be <= 0)
-#ifdef B200KV_DECODE_PROBE_NO_COMPUTE
-    if (false) {
-#else
     if (wtok > 0) {
-#endif
       const uint32_t kpage = stage_base + st * kStageBytes + warp * kPageBytes;
       const uint32_t vpage = kpage + kTileBytes;
       if (wtok < kPS) {

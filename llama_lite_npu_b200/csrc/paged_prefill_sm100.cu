@@ -492,19 +492,10 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
                 fma_f32x2(pack_u32x2(sr[c >> 5][c & 31], sr[(c + 1) >> 5][(c + 1) & 31]), scale2, negm2);
             float x0, x1;
             unpack_f32x2(x2, x0, x1);
-#ifdef B200KV_PREFILL_PROBE_NO_EX2
-            const float p0 = x0 * x0;
-            const float p1 = x1 * x1;
-#else
             const float p0 = fast_exp2(x0);
             const float p1 = fast_exp2(x1);
-#endif
             rs2[e & 1] = add_f32x2(rs2[e & 1], pack_f32x2(p0, p1));
-#ifdef B200KV_PREFILL_PROBE_NO_CVT
-            pk[e] = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
-#else
             pk[e] = pack_half2(p0, p1);
-#endif
           }
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(prow + ((ch ^ (row & 7)) << 4)),
                        "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
