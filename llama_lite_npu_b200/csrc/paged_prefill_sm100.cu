@@ -405,9 +405,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
     // O accumulates in TMEM.  The running maximum used to scale P and O (m_used) is only moved
     // when the true row maximum has grown by more than 8 (a factor 256, harmless for fp16 P and
     // fp32 accumulation): then O and l are rescaled once; otherwise a tile costs no pass over O.
-    // A 128-key S row is handled as two 64-column halves to stay within the register budget: both
-    // halves are read for the maximum, the second is exponentiated from registers, the first is
-    // re-read from TMEM (cheap) and exponentiated last.
+    // A thread holds its whole 128-column S row in registers: one TMEM round trip per tile.
     const int g = warp / kGroupWarps;                      // which query tile (head) of the pair
     const int gtid = tid - g * kGroupWarps * 32;
     const int row = gtid;                                  // query row of the tile = TMEM lane
@@ -427,28 +425,25 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       // Only tiles that reach past the first row's diagonal need the causal mask (warp-uniform).
       const bool need_mask = key0 + kBN - 1 > ctx + row0;
       const int lim = static_cast<int>(q_pos - key0 < kBN ? q_pos - key0 : kBN);  // keys c <= lim visible
-      uint32_t sr[2][32];
-      auto load_half = [&](int h) {
-        tmem_ld32(tmem_s + h * 64 + 0, sr[0]);
-        tmem_ld32(tmem_s + h * 64 + 32, sr[1]);
-        tmem_ld_wait();
-        if (need_mask) {
+      // The whole 128-column S row in one TMEM round trip (four loads in flight, one wait).
+      uint32_t sr[4][32];
+      tmem_ld32(tmem_s + 0, sr[0]);
+      tmem_ld32(tmem_s + 32, sr[1]);
+      tmem_ld32(tmem_s + 64, sr[2]);
+      tmem_ld32(tmem_s + 96, sr[3]);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c)
-            if (h * 64 + c > lim) sr[c >> 5][c & 31] = 0xff800000u;   // -inf
-        }
-      };
-      auto half_max = [&](float mx) {   // raw scores (the scale is positive), two per instruction
-#pragma unroll
-        for (int c = 0; c < 64; c += 2)
-          mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
-        return mx;
-      };
+        for (int c = 0; c < kBN; ++c)
+          if (c > lim) sr[c >> 5][c & 31] = 0xff800000u;   // -inf
+      }
+      // Row maximum of the RAW scores (the scale is positive), two new elements per instruction.
       float mx = -INFINITY;
-      load_half(0);
-      mx = half_max(mx);
-      load_half(1);
-      mx = half_max(mx) * p.scale_log2;
+#pragma unroll
+      for (int c = 0; c < kBN; c += 2)
+        mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+      mx *= p.scale_log2;
       // P_g and O_g are free once the P V MMAs of tile j-1 have completed (they were issued
       // before this tile's S, so this wait is normally already satisfied).
       if (j > 0 && !mbar_wait_bounded(b_pvfull, (j - 1) & 1)) { ok = false; break; }
@@ -480,14 +475,15 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       uint64_t rs2[2] = {pack_f32x2(0.f, 0.f), pack_f32x2(0.f, 0.f)};
       // P row -> shared memory, UMMA K-major layout with the 128-byte swizzle: 64-key chunk h is a
       // [128 rows][128 B] block, row r at r*128 B, its eight 16-byte pieces XOR-ed with r % 8.
-      auto exp_store_half = [&](int h) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
         const uint32_t prow = my_p + h * (kPBytes / 2) + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 8; ++ch) {
           uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int c = ch * 8 + 2 * e;
+            const int c = h * 64 + ch * 8 + 2 * e;
             const uint64_t x2 =
                 fma_f32x2(pack_u32x2(sr[c >> 5][c & 31], sr[(c + 1) >> 5][(c + 1) & 31]), scale2, negm2);
             float x0, x1;
@@ -501,11 +497,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
                        "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                        : "memory");
         }
-      };
-      exp_store_half(1);        // still in registers
-      load_half(0);
-      tc_fence_before();
-      exp_store_half(0);
+      }
       {
         float a0, a1, b0, b1;
         unpack_f32x2(rs2[0], a0, a1);
