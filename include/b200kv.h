@@ -108,6 +108,38 @@ int b200kv_kv_append_split(const void* k_values, const void* v_values,
                            int32_t* status, void* stream);
 
 /*
+ * Attention prologue in one launch: per-head RMSNorm of Q and K, rotary
+ * embedding of Q and K, and the scatter of K (normalised, rotated) and V (as
+ * is) into the pool.  Replaces, for one layer,
+ *   skip_rmsnorm(xq, None, q_norm_weight), skip_rmsnorm(xk, None, k_norm_weight)
+ *       lite_llama/models/qwen3.py:122-123, kernel lite_llama/kernels/skip_rmsnorm.py:118-144
+ *   rope_emb_forward(xq, xk, cos, sin)
+ *       lite_llama/models/qwen3.py:125-126, kernel lite_llama/kernels/rope_emb.py:6-87
+ *   torch.cat([xk, xv], dim=-2) + update_kv_buffer
+ *       lite_llama/models/qwen3.py:62-65 (decode), :29-32 (prefill)
+ *   q, q_out    fp16 [n_tokens, q_heads, head_dim]; q_out may be q (in place)
+ *   kv          fp16 [n_tokens, 2*kv_heads, head_dim]: the kv_proj output, K heads first
+ *   q_weight, k_weight  fp16 [head_dim] or NULL (NULL: that norm is skipped, as
+ *               for models without QK-norm, lite_llama/models/qwen2.py)
+ *   cos, sin    fp16 rows per token, token stride cs_tok_stride; only the first
+ *               head_dim/2 entries of a row are read (rope_emb.py:41-44)
+ *   slots, pool as for b200kv_kv_append
+ * Strides are in elements and must be multiples of 8; pointers 16-byte aligned;
+ * head_dim 64 or 128.  V rows and slots not named are bit-exact; Q and K follow
+ * the reference kernels' rounding (fp32 statistics, fp16(x*rrms)*w in fp16,
+ * rotation in fp32 rounded once).  n_tokens == 0 is a no-op.
+ */
+int b200kv_qk_norm_rope_append(const void* q, void* q_out, int64_t q_tok_stride,
+                               int64_t q_out_tok_stride,
+                               const void* kv, int64_t kv_tok_stride,
+                               const void* q_weight, const void* k_weight, float eps,
+                               const void* cos, const void* sin, int64_t cs_tok_stride,
+                               const int32_t* slots,
+                               void* pool, int64_t pool_tokens, int64_t pool_tok_stride,
+                               int64_t n_tokens, int q_heads, int kv_heads, int head_dim,
+                               int32_t* status, void* stream);
+
+/*
  * Bytes of scratch that b200kv_paged_decode needs for a batch of `batch`
  * sequences on the CURRENT device (split-KV partial outputs and their
  * log-sum-exp).  Depends on the device's SM count.  Returns 0 on bad input.

@@ -28,6 +28,16 @@ _SIGNATURES = {
         [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_int64,
          c_int, c_int, c_void_p, c_void_p],
     ),
+    "b200kv_qk_norm_rope_append": (
+        c_int,
+        [c_void_p, c_void_p, c_int64, c_int64,   # q, q_out, strides
+         c_void_p, c_int64,                      # kv
+         c_void_p, c_void_p, c_float,            # norm weights, eps
+         c_void_p, c_void_p, c_int64,            # cos, sin
+         c_void_p, c_void_p, c_int64, c_int64,   # slots, pool
+         c_int64, c_int, c_int, c_int,           # n_tokens, heads, dim
+         c_void_p, c_void_p],
+    ),
     "b200kv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200kv_paged_decode": (
         c_int,

@@ -82,6 +82,38 @@ int b200kv_kv_append_split(const void* k_values, const void* v_values, int64_t n
                                  static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_qk_norm_rope_append(const void* q, void* q_out, int64_t q_tok_stride,
+                               int64_t q_out_tok_stride, const void* kv, int64_t kv_tok_stride,
+                               const void* q_weight, const void* k_weight, float eps,
+                               const void* cos, const void* sin, int64_t cs_tok_stride,
+                               const int32_t* slots, void* pool, int64_t pool_tokens,
+                               int64_t pool_tok_stride, int64_t n_tokens, int q_heads,
+                               int kv_heads, int head_dim, int32_t* status, void* stream) {
+  b200kv::PrologueArgs a{};
+  a.q = q;
+  a.q_out = q_out;
+  a.q_tok_stride = q_tok_stride;
+  a.q_out_tok_stride = q_out_tok_stride;
+  a.kv = kv;
+  a.kv_tok_stride = kv_tok_stride;
+  a.q_weight = q_weight;
+  a.k_weight = k_weight;
+  a.eps = eps;
+  a.cos = cos;
+  a.sin = sin;
+  a.cs_tok_stride = cs_tok_stride;
+  a.slots = slots;
+  a.pool = pool;
+  a.pool_tokens = pool_tokens;
+  a.pool_tok_stride = pool_tok_stride;
+  a.n_tokens = n_tokens;
+  a.q_heads = q_heads;
+  a.kv_heads = kv_heads;
+  a.head_dim = head_dim;
+  a.status = status;
+  return b200kv::qk_norm_rope_append(a, static_cast<cudaStream_t>(stream));
+}
+
 size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
   return b200kv::decode_workspace_bytes(batch, q_heads, kv_heads, head_dim);
 }

@@ -21,6 +21,27 @@ int kv_append_split(const void* k_values, const void* v_values, int64_t n_tokens
                     int64_t pool_tokens, int64_t pool_tok_stride, int kv_heads, int head_dim,
                     int32_t* status, cudaStream_t stream);
 
+struct PrologueArgs {
+  const void* q;
+  void* q_out;
+  int64_t q_tok_stride, q_out_tok_stride;
+  const void* kv;
+  int64_t kv_tok_stride;
+  const void* q_weight;
+  const void* k_weight;
+  float eps;
+  const void* cos;
+  const void* sin;
+  int64_t cs_tok_stride;
+  const int32_t* slots;
+  void* pool;
+  int64_t pool_tokens, pool_tok_stride;
+  int64_t n_tokens;
+  int q_heads, kv_heads, head_dim;
+  int32_t* status;
+};
+int qk_norm_rope_append(const PrologueArgs& a, cudaStream_t stream);
+
 struct DecodeArgs {
   const void* q;
   int64_t q_stride_b, q_stride_h;

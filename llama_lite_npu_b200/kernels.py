@@ -33,6 +33,7 @@ _DEBUG = os.environ.get("B200KV_DEBUG", "0") not in ("", "0")
 
 _status: dict[int, torch.Tensor] = {}
 _workspace: dict[int, torch.Tensor] = {}
+_retired_workspaces: list[torch.Tensor] = []
 
 
 def _device_index(t: torch.Tensor) -> int:
@@ -130,6 +131,8 @@ def decode_workspace(device_index: int, batch: int, q_heads: int, kv_heads: int,
         )
     ws = _workspace.get(device_index)
     if ws is None or ws.numel() < need:
+        if ws is not None:
+            _retired_workspaces.append(ws)   # captured CUDA graphs may still point into it
         ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{device_index}")
         _workspace[device_index] = ws
     return ws
@@ -205,6 +208,64 @@ def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: tor
         )
     _lib.check(rc)
     _after_call(dev)
+
+
+@torch.no_grad()
+def fused_qk_norm_rope_append(xq: torch.Tensor, xkv: torch.Tensor, q_norm_weight: Optional[torch.Tensor],
+                              k_norm_weight: Optional[torch.Tensor], eps: float, cos: torch.Tensor,
+                              sin: torch.Tensor, Select_Index: torch.Tensor, KV_Buffer: torch.Tensor,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The attention prologue of one layer in one launch.
+
+    Equivalent to ``skip_rmsnorm(xq, None, q_norm_weight, eps)``, ``skip_rmsnorm(xk, None,
+    k_norm_weight, eps)``, ``rope_emb_forward(xq, xk, cos, sin, ...)`` and ``update_kv_buffer(
+    torch.cat([xk, xv], dim=-2), Select_Index, KV_Buffer)`` (``lite_llama/models/qwen3.py:109-126``
+    and ``:62-65``), with ``xk, xv`` the two halves of ``xkv``.
+
+    ``xq`` ``[n, q_heads, head_dim]`` is rewritten in place unless ``out`` is given; ``xkv`` is the
+    ``kv_proj`` output ``[n, 2*kv_heads*head_dim]`` (or ``[n, 2*kv_heads, head_dim]``) and is only
+    read; ``cos`` / ``sin`` are ``[..., head_dim]`` (or ``head_dim/2``) rows, one per token, as the
+    rotary embedding returns them.  A ``None`` weight skips that norm.  Returns the rotated Q.
+    """
+    dev = _device_index(KV_Buffer)
+    _require(xq.dim() == 3 and xq.dtype == torch.float16, "xq must be [n, q_heads, head_dim] float16")
+    n, qh, d = xq.shape
+    _require(KV_Buffer.dim() == 3 and KV_Buffer.dtype == torch.float16 and KV_Buffer.shape[2] == d
+             and KV_Buffer.shape[1] % 2 == 0, "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
+    rows = KV_Buffer.shape[1]
+    xkv = xkv.reshape(xkv.shape[0], -1) if xkv.dim() != 2 else xkv
+    _require(xkv.dtype == torch.float16 and xkv.shape[0] == n and xkv.shape[1] == rows * d
+             and xkv.stride(1) == 1, "xkv must be [n, 2*kv_heads*head_dim] float16, contiguous rows")
+    out = xq if out is None else out
+    _require(out.shape == xq.shape and out.dtype == torch.float16, "out must match xq")
+    for t, name in ((xq, "xq"), (out, "out"), (KV_Buffer, "KV_Buffer")):
+        _require(t.stride(2) == 1 and t.stride(1) == d, f"{name} must be contiguous inside a token")
+    cos2, sin2 = cos.reshape(-1, cos.shape[-1]), sin.reshape(-1, sin.shape[-1])
+    _require(cos2.dtype == torch.float16 and sin2.dtype == torch.float16, "cos and sin must be float16")
+    _require(cos2.shape == sin2.shape and cos2.shape[0] == n and cos2.shape[1] in (d, d // 2)
+             and cos2.stride(1) == 1 and sin2.stride(1) == 1 and cos2.stride(0) == sin2.stride(0),
+             "cos and sin must be one row of head_dim (or head_dim/2) per token with equal strides")
+    for w, name in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
+        _require(w is None or (w.dtype == torch.float16 and w.shape == (d,) and w.is_contiguous()),
+                 f"{name} must be a contiguous float16 [head_dim] tensor or None")
+    _require(Select_Index.dtype == torch.int32 and Select_Index.dim() == 1 and Select_Index.shape[0] == n,
+             "Select_Index must be a 1-D int32 tensor with one slot per token")
+    if n == 0:
+        return out
+    if not Select_Index.is_contiguous():
+        Select_Index = Select_Index.contiguous()
+    with _on_device(dev):
+        rc = _lib.lib().b200kv_qk_norm_rope_append(
+            xq.data_ptr(), out.data_ptr(), xq.stride(0), out.stride(0), xkv.data_ptr(), xkv.stride(0),
+            0 if q_norm_weight is None else q_norm_weight.data_ptr(),
+            0 if k_norm_weight is None else k_norm_weight.data_ptr(), float(eps),
+            cos2.data_ptr(), sin2.data_ptr(), cos2.stride(0), Select_Index.data_ptr(),
+            KV_Buffer.data_ptr(), KV_Buffer.shape[0], KV_Buffer.stride(0), n, qh, rows // 2, d,
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+    return out
 
 
 @torch.no_grad()

@@ -215,3 +215,41 @@ def token_table_from_block_table(block_table: torch.Tensor, page_size: int) -> t
     rows, width = block_table.shape
     off = torch.arange(page_size, dtype=torch.int64)
     return (block_table.long()[:, :, None] * page_size + off).reshape(rows, width * page_size).int()
+
+
+def head_rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """Per-head RMSNorm as the reference kernel rounds it (kernels/skip_rmsnorm.py:135-143):
+    float32 statistics (``sum(x*x/N)``), ``x * rrms`` rounded to fp16, then the fp16 product with
+    the weight.  ``weight is None`` returns ``x`` (models without QK-norm)."""
+    if weight is None:
+        return x
+    xf = x.float()
+    var = (xf * xf / x.shape[-1]).sum(dim=-1, keepdim=True)
+    rrms = 1.0 / torch.sqrt(var + eps)
+    return (xf * rrms).half() * weight.half()
+
+
+def rotate_halves(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x`` ``[n, heads, D]`` with one ``cos`` / ``sin`` row per token, of
+    which the first ``D/2`` entries are used (kernels/rope_emb.py:41-87):
+    ``o1 = x1*cos - x2*sin``, ``o2 = x2*cos + x1*sin`` on the two halves of the head.  Evaluated
+    in float32 from the fp16 values and rounded once (the reference evaluates it in the dtype of
+    ``cos``, which leaves the per-operation rounding to its compiler)."""
+    half = x.shape[-1] // 2
+    c = cos.reshape(x.shape[0], -1)[:, None, :half].float()
+    s = sin.reshape(x.shape[0], -1)[:, None, :half].float()
+    x1, x2 = x[..., :half].float(), x[..., half:].float()
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).half()
+
+
+def qk_norm_rope_append(xq, xkv, q_weight, k_weight, eps, cos, sin, select_index, kv_buffer) -> torch.Tensor:
+    """The attention prologue of one layer (models/qwen3.py:109-126 then :62-65): QK-RMSNorm,
+    rotary embedding, and the scatter of ``cat(xk, xv)`` into ``kv_buffer`` (in place).
+    ``xkv`` is the kv_proj output ``[n, 2*KH*D]``.  Returns the rotated Q ``[n, H, D]``."""
+    n, _, d = xq.shape
+    kvh = kv_buffer.shape[1] // 2
+    xk, xv = xkv.reshape(n, 2 * kvh, d)[:, :kvh], xkv.reshape(n, 2 * kvh, d)[:, kvh:]
+    q = rotate_halves(head_rmsnorm(xq, q_weight, eps), cos, sin)
+    k = rotate_halves(head_rmsnorm(xk, k_weight, eps), cos, sin)
+    kv_append(torch.cat([k, xv], dim=-2), select_index, kv_buffer)
+    return q

@@ -7,10 +7,14 @@ reference) and the tests (which run the oracle and the CUDA kernels) see identic
 
 from __future__ import annotations
 
+from pathlib import Path
+
 import numpy as np
 import torch
 
 from llama_lite_npu_b200 import workloads as W
+
+GOLDEN_DIR = Path(__file__).resolve().parent / "golden"
 
 # name -> (DecodeConfig, explicit lengths or None)
 DECODE_CASES = {
@@ -40,6 +44,14 @@ APPEND_CASES = {
     "append_decode": (4, 16, 8192),
     "append_prefill": (333, 4, 1024),
 }
+
+# name -> (tokens, q_heads, kv_heads, head_dim, pool_tokens, qk_norm)
+PROLOGUE_CASES = {
+    "prologue_qwen3_decode": (7, 8, 2, 128, 256, True),
+    "prologue_ragged_prefill": (33, 5, 1, 128, 512, True),
+    "prologue_d64_no_norm": (5, 4, 4, 64, 128, False),
+}
+PROLOGUE_EPS = 1e-6
 
 MHA_DECODE_CASES = {
     "decode_contiguous_mha": (3, 4, [50, 128, 77]),
@@ -76,6 +88,24 @@ def build_append(name: str, device="cpu"):
     pool = W.hash_normal_fp16(seed, (pool_tokens, rows, 128), 2).to(device)
     slots = torch.from_numpy(W.hash_permutation(seed, pool_tokens, 3)[:n].astype(np.int32)).to(device)
     return src, slots, pool
+
+
+def build_prologue(name: str, device="cpu"):
+    """Inputs of one attention prologue: Q, the kv_proj output, norm weights (or None), cos / sin
+    rows of full head_dim as the rotary module returns them, slots and the pool."""
+    n, qh, kvh, d, pool_tokens, norm = PROLOGUE_CASES[name]
+    seed = 61 + n
+    xq = W.hash_normal_fp16(seed, (n, qh, d), 1)
+    xkv = W.hash_normal_fp16(seed, (n, 2 * kvh * d), 2)
+    wq = (1.0 + 0.25 * W.hash_normal_fp16(seed, (d,), 3).float()).half() if norm else None
+    wk = (1.0 + 0.25 * W.hash_normal_fp16(seed, (d,), 4).float()).half() if norm else None
+    angles = 3.0 * W.hash_normal_fp16(seed, (n, d // 2), 5).float()
+    emb = torch.cat([angles, angles], dim=-1)
+    cos, sin = emb.cos().half(), emb.sin().half()
+    pool = W.hash_normal_fp16(seed, (pool_tokens, 2 * kvh, d), 6)
+    slots = torch.from_numpy(W.hash_permutation(seed, pool_tokens, 7)[:n].astype(np.int32))
+    mv = lambda t: None if t is None else t.to(device)  # noqa: E731
+    return mv(xq), mv(xkv), mv(wq), mv(wk), mv(cos), mv(sin), mv(slots), mv(pool)
 
 
 def build_mha_decode(name: str, device="cpu"):

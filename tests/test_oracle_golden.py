@@ -101,3 +101,41 @@ def test_token_table_expansion():
     bt = torch.tensor([[3, 7, 12]], dtype=torch.int32)
     tt = O.token_table_from_block_table(bt, 4)
     assert tt[0, :10].tolist() == [12, 13, 14, 15, 28, 29, 30, 31, 48, 49]
+
+
+def test_attention_prologue_matches_reference_statements():
+    """QK-RMSNorm + rotary embedding + scatter against the reference's torch statements.
+
+    Those statements work in fp16 throughout (the mean of squares and every product are rounded
+    to fp16) whereas the reference's kernels, and the oracle, keep float32 statistics; the
+    agreement is therefore a few fp16 units in the last place: 2e-3 absolute + 3e-3 relative.
+    V rows, and hence the scatter, are bit-exact."""
+    g = np.load(G.GOLDEN_DIR / "qk_prologue_golden.npz")
+    for name in G.PROLOGUE_CASES:
+        xq, xkv, wq, wk, cos, sin, slots, pool = G.build_prologue(name)
+        before = pool.clone()
+        q = O.qk_norm_rope_append(xq, xkv, wq, wk, G.PROLOGUE_EPS, cos, sin, slots, pool)
+        kvh = pool.shape[1] // 2
+        rows = pool[slots.long()]
+        want_q, want_rows = torch.from_numpy(g[f"{name}.q"]), torch.from_numpy(g[f"{name}.pool_rows"])
+        assert torch.allclose(q.float(), want_q.float(), atol=2e-3, rtol=3e-3), name
+        assert torch.allclose(rows[:, :kvh].float(), want_rows[:, :kvh].float(), atol=2e-3, rtol=3e-3), name
+        assert torch.equal(rows[:, kvh:], want_rows[:, kvh:]), name
+        untouched = torch.ones(pool.shape[0], dtype=torch.bool)
+        untouched[slots.long()] = False
+        assert torch.equal(pool[untouched], before[untouched]), name
+
+
+def test_rotation_preserves_norm_and_identity_angle():
+    """Two properties of the rotary statement: zero angle is the identity, and a rotation keeps
+    the length of every (x1[i], x2[i]) pair."""
+    x = G.W.hash_normal_fp16(7, (9, 3, 128), 1)
+    one, zero = torch.ones(9, 128, dtype=torch.float16), torch.zeros(9, 128, dtype=torch.float16)
+    assert torch.equal(O.rotate_halves(x, one, zero), x)
+    ang = 2.0 * G.W.hash_normal_fp16(7, (9, 64), 2).float()
+    emb = torch.cat([ang, ang], dim=-1)
+    y = O.rotate_halves(x, emb.cos().half(), emb.sin().half()).float()
+    xf = x.float()
+    r_in = xf[..., :64] ** 2 + xf[..., 64:] ** 2
+    r_out = y[..., :64] ** 2 + y[..., 64:] ** 2
+    assert torch.allclose(r_in, r_out, atol=2e-2, rtol=1e-2)
