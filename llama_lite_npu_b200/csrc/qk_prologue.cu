@@ -42,37 +42,48 @@ struct PrologueParams {
   const int32_t* slots;
   __half* pool;
   int64_t pool_tokens, pool_tok_stride;
-  int64_t n_tokens;
+  int n_tokens;
   int q_heads, kv_heads;
+  int groups_per_token;     // ceil((q_heads + 2*kv_heads) / rows per warp)
+  int step_tok, step_grp;   // (warps in the grid) / and % groups_per_token
   float eps;
   int32_t* status;
 };
 
-struct Vec8 {
-  float v[8];
-};
+__device__ __forceinline__ float2 h2f(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
 
-__device__ __forceinline__ Vec8 unpack8(const uint4& u) {
-  Vec8 r;
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
+// One 16-byte slice (8 halves) of a row: x*rrms rounded to fp16, times the fp16 weight in fp16.
+__device__ __forceinline__ void norm8(float (&x)[8], float rrms, const uint4& w) {
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(&w);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 f = __half22float2(h[i]);
-    r.v[2 * i] = f.x;
-    r.v[2 * i + 1] = f.y;
+    const __half2 y = __floats2half2_rn(x[2 * i] * rrms, x[2 * i + 1] * rrms);
+    const float2 f = __half22float2(__hmul2(y, *reinterpret_cast<const __half2*>(wp + i)));
+    x[2 * i] = f.x;
+    x[2 * i + 1] = f.y;
   }
-  return r;
 }
 
-__device__ __forceinline__ uint4 pack8(const Vec8& x) {
-  uint4 u;
-  u.x = pack_half2(x.v[0], x.v[1]);
-  u.y = pack_half2(x.v[2], x.v[3]);
-  u.z = pack_half2(x.v[4], x.v[5]);
-  u.w = pack_half2(x.v[6], x.v[7]);
-  return u;
+__device__ __forceinline__ void unpack8(const uint4& u, float (&x)[8]) {
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = h2f(p[i]);
+    x[2 * i] = f.x;
+    x[2 * i + 1] = f.y;
+  }
 }
 
+__device__ __forceinline__ uint4 pack8(const float (&x)[8]) {
+  return make_uint4(pack_half2(x[0], x[1]), pack_half2(x[2], x[3]), pack_half2(x[4], x[5]),
+                    pack_half2(x[6], x[7]));
+}
+
+// A warp takes one "group" of 32/kLanes consecutive head rows of ONE token per iteration, so the
+// token's slot, cos and sin are the same for the whole warp, and walks (token, group) pairs with
+// precomputed steps: no division in the loop.
 template <int D>
 __global__ void __launch_bounds__(kPrologueThreads) qk_prologue_kernel(PrologueParams p) {
   constexpr int kLanes = D / 16;            // lanes per head row
@@ -82,38 +93,49 @@ __global__ void __launch_bounds__(kPrologueThreads) qk_prologue_kernel(PrologueP
   cudaTriggerProgrammaticLaunchCompletion();
 
   const int lane = threadIdx.x & 31;
-  const int sub = lane % kLanes;            // position inside the row
+  const int sub = lane % kLanes;            // position inside the row: fixed for the thread
   const int rows_per_token = p.q_heads + 2 * p.kv_heads;
-  const int64_t total_rows = p.n_tokens * rows_per_token;
-  const int64_t warp = (static_cast<int64_t>(blockIdx.x) * kPrologueThreads + threadIdx.x) >> 5;
-  const int64_t n_warps = (static_cast<int64_t>(gridDim.x) * kPrologueThreads) >> 5;
+  const unsigned warp = (blockIdx.x * kPrologueThreads + threadIdx.x) >> 5;
+  int tok = static_cast<int>(warp / static_cast<unsigned>(p.groups_per_token));
+  int grp = static_cast<int>(warp % static_cast<unsigned>(p.groups_per_token));
 
-  for (int64_t base = warp * kRowsPerWarp; base < total_rows; base += n_warps * kRowsPerWarp) {
-    const int64_t row = base + lane / kLanes;
-    const bool live = row < total_rows;     // rows are padded to whole warps; dead lanes still shuffle
-    const int64_t tok = live ? row / rows_per_token : 0;
-    const int h = live ? static_cast<int>(row - tok * rows_per_token) : 0;
-    const bool is_q = h < p.q_heads;
-    const bool is_v = h >= p.q_heads + p.kv_heads;
+  // The thread's slice of both norm weights never changes: keep it in registers.
+  uint4 wq0, wq1, wk0, wk1;
+  wq0 = wq1 = wk0 = wk1 = make_uint4(0, 0, 0, 0);
+  if (p.q_weight != nullptr) {
+    wq0 = __ldg(reinterpret_cast<const uint4*>(p.q_weight + sub * 8));
+    wq1 = __ldg(reinterpret_cast<const uint4*>(p.q_weight + kHalf + sub * 8));
+  }
+  if (p.k_weight != nullptr) {
+    wk0 = __ldg(reinterpret_cast<const uint4*>(p.k_weight + sub * 8));
+    wk1 = __ldg(reinterpret_cast<const uint4*>(p.k_weight + kHalf + sub * 8));
+  }
 
-    const __half* src = is_q ? p.q + tok * p.q_tok_stride + static_cast<int64_t>(h) * D
-                             : p.kv + tok * p.kv_tok_stride + static_cast<int64_t>(h - p.q_heads) * D;
-    uint4 ua = make_uint4(0, 0, 0, 0), ub = ua;
-    if (live) {
-      ua = __ldg(reinterpret_cast<const uint4*>(src + sub * 8));
-      ub = __ldg(reinterpret_cast<const uint4*>(src + kHalf + sub * 8));
-    }
+  for (; tok < p.n_tokens;) {
+    const int h = grp * kRowsPerWarp + lane / kLanes;
+    const bool live = h < rows_per_token;   // the last group of a token may be ragged
+    const int kind = h < p.q_heads ? 0 : (h < p.q_heads + p.kv_heads ? 1 : 2);   // Q, K, V row
+    const int64_t t = tok;
 
+    uint4 ua = make_uint4(0, 0, 0, 0), ub = ua, uc = ua, us = ua;
     __half* dst = nullptr;
     if (live) {
-      if (is_q) {
-        dst = p.q_out + tok * p.q_out_tok_stride + static_cast<int64_t>(h) * D;
+      const __half* src = kind == 0 ? p.q + t * p.q_tok_stride + h * D
+                                    : p.kv + t * p.kv_tok_stride + (h - p.q_heads) * D;
+      ua = __ldg(reinterpret_cast<const uint4*>(src + sub * 8));
+      ub = __ldg(reinterpret_cast<const uint4*>(src + kHalf + sub * 8));
+      if (kind != 2) {
+        uc = __ldg(reinterpret_cast<const uint4*>(p.cos + t * p.cs_tok_stride + sub * 8));
+        us = __ldg(reinterpret_cast<const uint4*>(p.sin + t * p.cs_tok_stride + sub * 8));
+      }
+      if (kind == 0) {
+        dst = p.q_out + t * p.q_out_tok_stride + h * D;
       } else {
         const int64_t slot = __ldg(p.slots + tok);
         if (slot < 0 || slot >= p.pool_tokens) {
           set_status(p.status, B200KV_DEV_BAD_SLOT);
         } else {
-          dst = p.pool + slot * p.pool_tok_stride + static_cast<int64_t>(h - p.q_heads) * D;
+          dst = p.pool + slot * p.pool_tok_stride + (h - p.q_heads) * D;
         }
       }
     }
@@ -121,43 +143,45 @@ __global__ void __launch_bounds__(kPrologueThreads) qk_prologue_kernel(PrologueP
     // Sum of squares over the row.  The row's kLanes lanes are consecutive, so xor-shuffles below
     // kLanes stay inside it; every lane of the warp takes part (V rows and dead lanes too), which
     // keeps the shuffle outside any divergent branch.
-    Vec8 a = unpack8(ua), b = unpack8(ub);
+    float a[8], b[8];
+    unpack8(ua, a);
+    unpack8(ub, b);
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) ss += a.v[i] * a.v[i] + b.v[i] * b.v[i];
+    for (int i = 0; i < 8; ++i) ss += a[i] * a[i] + b[i] * b[i];
 #pragma unroll
     for (int m = 1; m < kLanes; m <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);
 
-    if (!is_v) {
-      const __half* w = is_q ? p.q_weight : p.k_weight;
-      if (w != nullptr) {
-        const float rrms = 1.0f / sqrtf(ss * (1.0f / D) + p.eps);
-        const uint4 wa_u = __ldg(reinterpret_cast<const uint4*>(w + sub * 8));
-        const uint4 wb_u = __ldg(reinterpret_cast<const uint4*>(w + kHalf + sub * 8));
-        const __half* wa = reinterpret_cast<const __half*>(&wa_u);
-        const __half* wb = reinterpret_cast<const __half*>(&wb_u);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          a.v[i] = __half2float(__hmul(__float2half_rn(a.v[i] * rrms), wa[i]));
-          b.v[i] = __half2float(__hmul(__float2half_rn(b.v[i] * rrms), wb[i]));
-        }
+    if (kind != 2) {
+      if ((kind == 0 ? p.q_weight : p.k_weight) != nullptr) {
+        // correctly rounded sqrt and divide: the fast-math forms would move more values across
+        // an fp16 rounding boundary than the summation order already does
+        const float rrms = __fdiv_rn(1.0f, __fsqrt_rn(ss * (1.0f / D) + p.eps));
+        norm8(a, rrms, kind == 0 ? wq0 : wk0);
+        norm8(b, rrms, kind == 0 ? wq1 : wk1);
       }
-      const __half* crow = p.cos + tok * p.cs_tok_stride + sub * 8;
-      const __half* srow = p.sin + tok * p.cs_tok_stride + sub * 8;
-      const Vec8 c = unpack8(__ldg(reinterpret_cast<const uint4*>(crow)));
-      const Vec8 s = unpack8(__ldg(reinterpret_cast<const uint4*>(srow)));
-      Vec8 oa, ob;
+      float c[8], s[8];
+      unpack8(uc, c);
+      unpack8(us, s);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        oa.v[i] = a.v[i] * c.v[i] - b.v[i] * s.v[i];
-        ob.v[i] = b.v[i] * c.v[i] + a.v[i] * s.v[i];
+        const float x1 = a[i], x2 = b[i];
+        a[i] = x1 * c[i] - x2 * s[i];
+        b[i] = x2 * c[i] + x1 * s[i];
       }
-      ua = pack8(oa);
-      ub = pack8(ob);
+      ua = pack8(a);
+      ub = pack8(b);
     }
     if (dst != nullptr) {
       *reinterpret_cast<uint4*>(dst + sub * 8) = ua;
       *reinterpret_cast<uint4*>(dst + kHalf + sub * 8) = ub;
+    }
+
+    tok += p.step_tok;
+    grp += p.step_grp;
+    if (grp >= p.groups_per_token) {
+      grp -= p.groups_per_token;
+      ++tok;
     }
   }
 }
@@ -165,14 +189,19 @@ __global__ void __launch_bounds__(kPrologueThreads) qk_prologue_kernel(PrologueP
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <int D>
-int launch(const PrologueParams& p, cudaStream_t stream) {
-  constexpr int kRowsPerBlock = (kPrologueThreads / 32) * (32 / (D / 16));
-  const int64_t total_rows = p.n_tokens * (p.q_heads + 2 * p.kv_heads);
+int launch(PrologueParams p, cudaStream_t stream) {
+  constexpr int kRowsPerWarp = 32 / (D / 16);
+  constexpr int kWarpsPerBlock = kPrologueThreads / 32;
+  p.groups_per_token = (p.q_heads + 2 * p.kv_heads + kRowsPerWarp - 1) / kRowsPerWarp;
+  const int64_t groups = static_cast<int64_t>(p.n_tokens) * p.groups_per_token;
   const int sms = device_sm_count();
   if (sms <= 0) return B200KV_ECUDA;
-  int64_t blocks = (total_rows + kRowsPerBlock - 1) / kRowsPerBlock;
-  const int64_t cap = static_cast<int64_t>(sms) * 8;   // 8 resident CTAs of 256 threads per SM
+  int64_t blocks = (groups + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  const int64_t cap = static_cast<int64_t>(sms) * 8;   // grid-stride above 8 CTAs of 256 threads per SM
   if (blocks > cap) blocks = cap;
+  const int64_t n_warps = blocks * kWarpsPerBlock;
+  p.step_tok = static_cast<int>(n_warps / p.groups_per_token);
+  p.step_grp = static_cast<int>(n_warps % p.groups_per_token);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -193,6 +222,7 @@ int qk_norm_rope_append(const PrologueArgs& a, cudaStream_t stream) {
   if (a.n_tokens < 0 || a.q_heads <= 0 || a.kv_heads <= 0 || a.pool_tokens < 0) return B200KV_EINVAL;
   if (a.head_dim != 64 && a.head_dim != 128) return B200KV_EUNSUPPORTED;
   if (a.n_tokens == 0) return B200KV_OK;
+  if (a.n_tokens > (1 << 30)) return B200KV_ETOOLARGE;
   if (!a.q || !a.q_out || !a.kv || !a.cos || !a.sin || !a.slots || !a.pool) return B200KV_EINVAL;
   if (!(a.eps >= 0.f)) return B200KV_EINVAL;
   const int64_t d = a.head_dim;
@@ -223,7 +253,7 @@ int qk_norm_rope_append(const PrologueArgs& a, cudaStream_t stream) {
   p.pool = static_cast<__half*>(a.pool);
   p.pool_tokens = a.pool_tokens;
   p.pool_tok_stride = a.pool_tok_stride;
-  p.n_tokens = a.n_tokens;
+  p.n_tokens = static_cast<int>(a.n_tokens);
   p.q_heads = a.q_heads;
   p.kv_heads = a.kv_heads;
   p.eps = a.eps;

@@ -344,3 +344,39 @@ class PagedKVExecutor:
         return kernels.flash_decoding(
             xq, pool[:, :kh, :], pool[:, kh:, :], qk_scale, info.b_req_block_table, info.b_seq_len,
             info.max_actual_seq_len, b_req_idx=info.b_req_idx, table_kind="block")
+
+    # ------------------------------------------------------------------ fused prologue variants
+    def fused_token_forward(self, xq, xkv, q_norm_weight, k_norm_weight, eps: float, cos, sin,
+                            layer_index: int, qk_scale: float) -> torch.Tensor:
+        """Decode attention of one layer from the raw projections: QK-RMSNorm, rotary embedding
+        and the KV append in one launch, then paged decode.  ``xq`` is rewritten in place;
+        ``xkv`` is the kv_proj output ``[batch, 2*kv_heads*head_dim]``.  Same result as
+        normalising and rotating first and calling ``token_forward``
+        (``lite_llama/models/qwen3.py:109-130`` followed by ``:53-75``)."""
+        from . import kernels
+
+        info, kh = self.atten_info, self.num_kv_heads
+        pool = info.kv_buffer[layer_index]
+        kernels.fused_qk_norm_rope_append(xq, xkv, q_norm_weight, k_norm_weight, eps, cos, sin,
+                                          info.cur_select_index, pool)
+        return kernels.flash_decoding(
+            xq, pool[:, :kh, :], pool[:, kh:, :], qk_scale, info.b_req_block_table, info.b_seq_len,
+            info.max_actual_seq_len, b_req_idx=info.b_req_idx, table_kind="block")
+
+    def fused_context_forward(self, xq, xkv, q_norm_weight, k_norm_weight, eps: float, cos, sin,
+                              layer_index: int, qk_scale: float) -> torch.Tensor:
+        """Prefill attention of one layer from the raw projections (see ``fused_token_forward``);
+        ``qk_scale`` is the softmax scale times log2(e) as for ``context_forward``."""
+        from . import kernels
+
+        info, kh = self.atten_info, self.num_kv_heads
+        pool = info.kv_buffer[layer_index]
+        kernels.fused_qk_norm_rope_append(xq, xkv, q_norm_weight, k_norm_weight, eps, cos, sin,
+                                          info.cur_select_index, pool)
+        if info.is_paged_chunk_prefill:
+            ctx, qlen, max_q = info.chunk_context_len, info.chunk_q_seq_len, info.max_actual_q_seq_len
+        else:
+            ctx, qlen, max_q = torch.zeros_like(info.b_seq_len), info.b_seq_len, info.max_actual_seq_len
+        return kernels.paged_chunk_flash_attention(
+            xq, pool[:, :kh, :], pool[:, kh:, :], qk_scale, info.b_req_block_table, info.b_req_idx,
+            info.b_start_loc, ctx, qlen, max_q, table_kind="block")

@@ -139,7 +139,59 @@ def test_prologue_prefill_size_against_torch_on_device():
     want_pool = pool.clone()
     want_q = O.qk_norm_rope_append(xq, xkv, wq, wk, 1e-6, cos, sin, slots, want_pool)
     got = kernels.fused_qk_norm_rope_append(xq, xkv, wq, wk, 1e-6, cos, sin, slots, pool)
-    assert torch.allclose(got.float(), want_q.float(), atol=1e-3, rtol=1e-3)
-    assert torch.allclose(pool[:, :kvh].float(), want_pool[:, :kvh].float(), atol=1e-3, rtol=1e-3)
+    # Among 7e7 values some normalised ones sit on an fp16 rounding boundary and land on the other
+    # side when the sum of squares is added up in another order; the rotation then carries that
+    # one unit (up to 2^-8 for |x| in [4, 8)) into an output of any size.  So: an absolute bound of
+    # one such unit, and bounds on how often and how much on average the results differ at all.
+    for a, b in ((got, want_q), (pool[:, :kvh], want_pool[:, :kvh])):
+        diff = (a.float() - b.float()).abs()
+        assert float(diff.max()) <= 2.0 ** -8 + 1e-3
+        assert float((diff > 0).float().mean()) < 5e-3
+        assert float(diff.mean()) < 2e-6
     assert torch.equal(pool[:, kvh:], want_pool[:, kvh:])
     assert math.isfinite(float(got.float().abs().max()))
+
+
+def test_executor_fused_forward_equals_norm_rope_then_forward():
+    """Prefill of two prompts and two decode steps from raw projections through the fused calls,
+    against the oracle's norm + rotation followed by the executor's unfused calls on a twin pool."""
+    from llama_lite_npu_b200.executor import PagedKVExecutor
+
+    kvh, heads, d, eps = 2, 8, 128, 1e-6
+    scale = 1.0 / math.sqrt(d)
+    twins = [PagedKVExecutor(1, kvh, d, 64, 4, 256, page_size=16, device=DEV) for _ in range(2)]
+    wq = (1 + 0.1 * W.hash_normal_fp16(21, (d,), 1).float()).half().to(DEV)
+    wk = (1 + 0.1 * W.hash_normal_fp16(21, (d,), 2).float()).half().to(DEV)
+
+    def inputs(n, seed):
+        xq = W.hash_normal_fp16(seed, (n, heads, d), 1).to(DEV)
+        xkv = W.hash_normal_fp16(seed, (n, 2 * kvh * d), 2).to(DEV)
+        ang = W.hash_normal_fp16(seed, (n, d // 2), 3).float()
+        emb = torch.cat([ang, ang], dim=-1)
+        return xq, xkv, emb.cos().half().to(DEV), emb.sin().half().to(DEV)
+
+    def unfused(ex, xq, xkv, cos, sin, forward, sc):
+        n = xq.shape[0]
+        kv = xkv.view(n, 2 * kvh, d)
+        q = O.rotate_halves(O.head_rmsnorm(xq, wq, eps), cos, sin)
+        k = O.rotate_halves(O.head_rmsnorm(kv[:, :kvh], wk, eps), cos, sin)
+        return forward(q, k, kv[:, kvh:].contiguous(), 0, sc)
+
+    lens = [37, 50]
+    ids = [ex.reserve_paged_requests(lens) for ex in twins]
+    for ex, i in zip(twins, ids):
+        ex.activate_paged_packed_prefill_batch(i, lens)
+    xq, xkv, cos, sin = inputs(sum(lens), 31)
+    want = unfused(twins[1], xq, xkv, cos, sin, twins[1].context_forward, scale * 1.4426950408889634)
+    got = twins[0].fused_context_forward(xq.clone(), xkv, wq, wk, eps, cos, sin, 0, scale * 1.4426950408889634)
+    assert float((got.float() - want.float()).abs().max()) <= 2e-3
+    for step in range(2):
+        for ex, i in zip(twins, ids):
+            ex.extend_paged_requests(i)
+        xq, xkv, cos, sin = inputs(2, 40 + step)
+        want = unfused(twins[1], xq, xkv, cos, sin, twins[1].token_forward, scale)
+        got = twins[0].fused_token_forward(xq.clone(), xkv, wq, wk, eps, cos, sin, 0, scale)
+        assert float((got.float() - want.float()).abs().max()) <= 2e-3
+    p0, p1 = (ex.kv_mem_manager.gpu_kv_buffer[0] for ex in twins)
+    assert torch.allclose(p0.float(), p1.float(), atol=1e-3, rtol=1e-3)
+    assert torch.equal(p0[:, kvh:], p1[:, kvh:])
