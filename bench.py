@@ -239,9 +239,24 @@ def run_b200(args, cfg_full):
         g.manual_seed(cfg.seed * 977 + i)
         p.normal_(generator=g)
 
+    if args.prologue:
+        # the step starts from the raw projections: QK-RMSNorm + rotary embedding + append, fused
+        g = torch.Generator(device=dev)
+        g.manual_seed(cfg.seed + 5)
+        d = cfg.head_dim
+        raw_q = torch.randn(case.q.shape, device=dev, dtype=torch.float16, generator=g)
+        raw_kv = case.new_kv.reshape(case.new_kv.shape[0], -1)
+        norm_w = (1 + 0.1 * torch.randn(2, d, device=dev, generator=g)).half()
+        ang = torch.rand(case.q.shape[0], d // 2, device=dev, generator=g) * 6.283
+        cos, sin = ang.cos().half(), ang.sin().half()
+
     def step(i):
         pool = pools[i % layers]
-        kernels.update_kv_buffer(case.new_kv, case.slots, pool)
+        if args.prologue:
+            kernels.fused_qk_norm_rope_append(raw_q, raw_kv, norm_w[0], norm_w[1], 1e-6, cos, sin,
+                                              case.slots, pool, out=case.q)
+        else:
+            kernels.update_kv_buffer(case.new_kv, case.slots, pool)
         return kernels.flash_decoding(case.q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
                                       case.seq_lens_t, case.max_len, table_kind="block")
 
@@ -370,7 +385,10 @@ def run_b200(args, cfg_full):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic", "config": workload_config(cfg_full, world, layers),
+            "data": "synthetic",
+            "config": dict(workload_config(cfg_full, world, layers),
+                           **({"step_prologue": "fused QK-RMSNorm + rotary embedding + KV append"}
+                              if args.prologue else {})),
             "bytes_per_step": job_bytes,
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -556,6 +574,9 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prologue", action="store_true",
+                    help="decode workloads: start each step from raw projections (fused QK-RMSNorm + "
+                         "rotary embedding + KV append) instead of the plain KV append")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if isinstance(cfg, W.PrefillConfig):

@@ -160,6 +160,8 @@ def test_executor_fused_forward_equals_norm_rope_then_forward():
     kvh, heads, d, eps = 2, 8, 128, 1e-6
     scale = 1.0 / math.sqrt(d)
     twins = [PagedKVExecutor(1, kvh, d, 64, 4, 256, page_size=16, device=DEV) for _ in range(2)]
+    for ex in twins:
+        ex.kv_mem_manager.gpu_kv_buffer[0].zero_()           # the pools are compared whole at the end
     wq = (1 + 0.1 * W.hash_normal_fp16(21, (d,), 1).float()).half().to(DEV)
     wk = (1 + 0.1 * W.hash_normal_fp16(21, (d,), 2).float()).half().to(DEV)
 
