@@ -140,6 +140,30 @@ int b200kv_qk_norm_rope_append(const void* q, void* q_out, int64_t q_tok_stride,
                                int32_t* status, void* stream);
 
 /*
+ * Decode-step batch metadata on the device.  For every sequence b of the batch
+ * (table row r = req_ids[b], or b when req_ids is NULL), with pos = seq_lens[b]:
+ *   slots[b]     = block_table[r][pos / page_size] * page_size + pos % page_size
+ *   token_table[r][pos] = slots[b]            (when token_table is not NULL)
+ *   seq_lens[b]  = pos + 1
+ * i.e. what the reference computes on the host, request by request, before each
+ * decode step: extend_req (lite_llama/executor/paged_attention.py:313-359) and
+ * batch_metadata (:287-311), called from extend_paged_requests /
+ * activate_paged_decode_batch (lite_llama/executor/model_executor.py:893-931).
+ * The page for position pos must already be in the block table (the host
+ * allocates it when a page boundary is crossed); page_counts, when not NULL,
+ * gives the pages present per table row and lets the kernel refuse
+ * (B200KV_DEV_BAD_LENGTH, nothing written for that sequence) instead of
+ * reading a stale entry.  Integer work, bit-exact.
+ */
+int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i64,
+                          int32_t* slots,
+                          const int32_t* block_table, int64_t block_row_stride,
+                          int table_rows, int table_pages, const int32_t* page_counts,
+                          int32_t* token_table, int64_t token_row_stride, int token_cols,
+                          int batch, int page_size, int64_t pool_pages,
+                          int32_t* status, void* stream);
+
+/*
  * Bytes of scratch that b200kv_paged_decode needs for a batch of `batch`
  * sequences on the CURRENT device (split-KV partial outputs and their
  * log-sum-exp).  Depends on the device's SM count.  Returns 0 on bad input.

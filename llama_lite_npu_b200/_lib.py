@@ -38,6 +38,13 @@ _SIGNATURES = {
          c_int64, c_int, c_int, c_int,           # n_tokens, heads, dim
          c_void_p, c_void_p],
     ),
+    "b200kv_decode_advance": (
+        c_int,
+        [c_void_p, c_void_p, c_int, c_void_p,            # req_ids, seq_lens, slots
+         c_void_p, c_int64, c_int, c_int, c_void_p,      # block table, page_counts
+         c_void_p, c_int64, c_int,                       # token table
+         c_int, c_int, c_int64, c_void_p, c_void_p],
+    ),
     "b200kv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200kv_paged_decode": (
         c_int,

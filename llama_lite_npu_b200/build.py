@@ -22,7 +22,9 @@ STAMP_PATH = PKG_DIR / "libb200kv.stamp"
 
 SOURCES = (
     "b200kv_capi.cu",
-    "kv_append.cu", "qk_prologue.cu",
+    "kv_append.cu",
+    "qk_prologue.cu",
+    "batch_metadata.cu",
     "paged_decode.cu",
     "tma.cu",
     "paged_prefill_sm100.cu",

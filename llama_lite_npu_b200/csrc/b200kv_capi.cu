@@ -114,6 +114,31 @@ int b200kv_qk_norm_rope_append(const void* q, void* q_out, int64_t q_tok_stride,
   return b200kv::qk_norm_rope_append(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i64, int32_t* slots,
+                          const int32_t* block_table, int64_t block_row_stride, int table_rows,
+                          int table_pages, const int32_t* page_counts, int32_t* token_table,
+                          int64_t token_row_stride, int token_cols, int batch, int page_size,
+                          int64_t pool_pages, int32_t* status, void* stream) {
+  b200kv::AdvanceArgs a{};
+  a.req_ids = req_ids;
+  a.seq_lens = seq_lens;
+  a.seq_lens_i64 = seq_lens_i64;
+  a.slots = slots;
+  a.block_table = block_table;
+  a.block_row_stride = block_row_stride;
+  a.table_rows = table_rows;
+  a.table_pages = table_pages;
+  a.page_counts = page_counts;
+  a.token_table = token_table;
+  a.token_row_stride = token_row_stride;
+  a.token_cols = token_cols;
+  a.batch = batch;
+  a.page_size = page_size;
+  a.pool_pages = pool_pages;
+  a.status = status;
+  return b200kv::decode_advance(a, static_cast<cudaStream_t>(stream));
+}
+
 size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
   return b200kv::decode_workspace_bytes(batch, q_heads, kv_heads, head_dim);
 }

@@ -42,6 +42,24 @@ struct PrologueArgs {
 };
 int qk_norm_rope_append(const PrologueArgs& a, cudaStream_t stream);
 
+struct AdvanceArgs {
+  const int32_t* req_ids;
+  void* seq_lens;
+  int seq_lens_i64;
+  int32_t* slots;
+  const int32_t* block_table;
+  int64_t block_row_stride;
+  int table_pages;
+  const int32_t* page_counts;
+  int32_t* token_table;
+  int64_t token_row_stride;
+  int token_cols;
+  int batch, table_rows, page_size;
+  int64_t pool_pages;
+  int32_t* status;
+};
+int decode_advance(const AdvanceArgs& a, cudaStream_t stream);
+
 struct DecodeArgs {
   const void* q;
   int64_t q_stride_b, q_stride_h;

@@ -315,6 +315,34 @@ class PagedKVExecutor:
                     f"max_seq_len={mgr.max_seq_len}, free_pages={mgr.page_mgr.num_free_pages}")
         self.activate_paged_decode_batch(request_ids)
 
+    def extend_paged_requests_on_device(self, request_ids: tuple[int, ...]) -> None:
+        """``extend_paged_requests`` with the per-step metadata produced on the device.
+
+        When the batch is the one that is already active, its ``b_seq_len`` / ``cur_select_index``
+        tensors are advanced in place by one small kernel: nothing is copied from the host unless a
+        sequence crossed a page boundary (then only the new block-table entry is).  The tensors
+        keep their addresses, so a captured decode step can be replayed as is.  Any other batch
+        goes through the host path once, which also makes it the active one."""
+        if tuple(request_ids) != self._paged_request_ids or self.atten_info.b_seq_len is None:
+            self.extend_paged_requests(request_ids)
+            return
+        from . import kernels
+
+        mgr = self.req_tokens_manager
+        failed = mgr.extend_batch_for_device(request_ids)
+        if failed is not None:
+            raise RuntimeError(
+                "Paged KV allocation failed for request "
+                f"{failed}: current_tokens={mgr.req_token_count.get(failed, 'unknown')}, "
+                f"max_seq_len={mgr.max_seq_len}, free_pages={mgr.page_mgr.num_free_pages}")
+        info = self.atten_info
+        self._publish_tables()                                   # flushes a new page entry, if any
+        kernels.advance_decode_metadata(
+            info.b_seq_len, info.cur_select_index, info.b_req_block_table, self.page_size,
+            self.kv_mem_manager.num_pages, b_req_idx=info.b_req_idx, page_counts=mgr.page_counts,
+            b_req_tokens_table=info.b_req_tokens_table)
+        info.max_actual_seq_len += 1
+
     # ------------------------------------------------------------------ attention call sequences
     def context_forward(self, xq, xk, xv, layer_index: int, qk_scale: float) -> torch.Tensor:
         """Prefill attention of one layer: append the chunk's K/V, then attend.  ``qk_scale`` is the

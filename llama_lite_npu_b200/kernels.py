@@ -211,6 +211,53 @@ def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: tor
 
 
 @torch.no_grad()
+def advance_decode_metadata(b_seq_len: torch.Tensor, cur_select_index: torch.Tensor,
+                            b_req_block_table: torch.Tensor, page_size: int, num_pages: int, *,
+                            b_req_idx: Optional[torch.Tensor] = None,
+                            page_counts: Optional[torch.Tensor] = None,
+                            b_req_tokens_table: Optional[torch.Tensor] = None) -> None:
+    """Advance a decode batch by one token on the device, in place.
+
+    ``b_seq_len[b]`` (int32 or int64) becomes ``b_seq_len[b] + 1`` and ``cur_select_index[b]``
+    the slot of the new token, looked up in ``b_req_block_table`` (row ``b_req_idx[b]``, or ``b``);
+    ``b_req_tokens_table`` (optional) gets the new entry too.  The device-side form of the
+    reference's per-request ``extend_req`` + ``batch_metadata``
+    (``lite_llama/executor/paged_attention.py:287-359``); the page of the new token must already
+    be in the block table (``page_counts`` lets the kernel check that)."""
+    dev = _device_index(b_req_block_table)
+    _, i64 = _lens_arg(b_seq_len, "b_seq_len")
+    n = b_seq_len.shape[0]
+    _require(cur_select_index.dtype == torch.int32 and cur_select_index.shape == (n,)
+             and cur_select_index.is_contiguous(), "cur_select_index must be int32 [batch], contiguous")
+    _require(b_req_block_table.dtype == torch.int32 and b_req_block_table.dim() == 2
+             and b_req_block_table.stride(1) == 1, "b_req_block_table must be a 2-D int32 tensor")
+    for t, name in ((b_req_idx, "b_req_idx"), (page_counts, "page_counts")):
+        _require(t is None or (t.dtype == torch.int32 and t.dim() == 1 and t.is_contiguous()),
+                 f"{name} must be a contiguous 1-D int32 tensor")
+    _require(b_req_idx is None or b_req_idx.shape[0] == n, "b_req_idx must have one entry per sequence")
+    _require(page_counts is None or page_counts.shape[0] == b_req_block_table.shape[0],
+             "page_counts must have one entry per table row")
+    tt = b_req_tokens_table
+    _require(tt is None or (tt.dtype == torch.int32 and tt.dim() == 2 and tt.stride(1) == 1
+                            and tt.shape[0] == b_req_block_table.shape[0]),
+             "b_req_tokens_table must be a 2-D int32 tensor with the block table's rows")
+    if n == 0:
+        return
+    with _on_device(dev):
+        rc = _lib.lib().b200kv_decode_advance(
+            0 if b_req_idx is None else b_req_idx.data_ptr(), b_seq_len.data_ptr(), i64,
+            cur_select_index.data_ptr(), b_req_block_table.data_ptr(), b_req_block_table.stride(0),
+            b_req_block_table.shape[0], b_req_block_table.shape[1],
+            0 if page_counts is None else page_counts.data_ptr(),
+            0 if tt is None else tt.data_ptr(), 0 if tt is None else tt.stride(0),
+            0 if tt is None else tt.shape[1], n, int(page_size), int(num_pages),
+            status_tensor(dev).data_ptr(), _stream(dev),
+        )
+    _lib.check(rc)
+    _after_call(dev)
+
+
+@torch.no_grad()
 def fused_qk_norm_rope_append(xq: torch.Tensor, xkv: torch.Tensor, q_norm_weight: Optional[torch.Tensor],
                               k_norm_weight: Optional[torch.Tensor], eps: float, cos: torch.Tensor,
                               sin: torch.Tensor, Select_Index: torch.Tensor, KV_Buffer: torch.Tensor,

@@ -25,6 +25,7 @@ import bisect
 import heapq
 from typing import List, Optional, Tuple
 
+import numpy as np
 import torch
 
 
@@ -150,6 +151,11 @@ class PagedReqTokensManager:
         else:
             self._dev_tokens = self._host_tokens
             self._dev_blocks = self._host_blocks
+        # pages present per table row (what the device-side metadata kernel checks against)
+        self._host_page_counts = torch.zeros(max_requests, dtype=torch.int32, pin_memory=on_gpu)
+        self._dev_page_counts = (torch.zeros(max_requests, dtype=torch.int32, device=device)
+                                 if on_gpu else self._host_page_counts)
+        self._dirty_counts = False
         self._dirty_tokens: list[tuple[int, int, int]] = []  # (row, start, end) token spans
         self._dirty_blocks: list[tuple[int, int, int]] = []  # (row, start, end) page spans
 
@@ -171,12 +177,22 @@ class PagedReqTokensManager:
         self.flush()
         return self._dev_blocks
 
+    @property
+    def page_counts(self) -> torch.Tensor:
+        """int32 ``[max_requests]`` on the device: pages present in each block-table row."""
+        self.flush()
+        return self._dev_page_counts
+
     def flush(self) -> None:
         """Push pending table edits to the device: one index buffer, one value buffer per table."""
         if not self._lazy:
             self._dirty_tokens.clear()
             self._dirty_blocks.clear()
+            self._dirty_counts = False
             return
+        if self._dirty_counts:
+            self._dev_page_counts.copy_(self._host_page_counts, non_blocking=True)
+            self._dirty_counts = False
         for dirty, host, dev in (
             (self._dirty_tokens, self._host_tokens, self._dev_tokens),
             (self._dirty_blocks, self._host_blocks, self._dev_blocks),
@@ -199,6 +215,8 @@ class PagedReqTokensManager:
         if first_page < len(pages):
             self._host_blocks[req_idx, first_page:len(pages)] = pages[first_page:].to(torch.int32)
             self._dirty_blocks.append((req_idx, first_page, len(pages)))
+        self._host_page_counts[req_idx] = len(pages)
+        self._dirty_counts = True
 
     def _write_tokens(self, req_idx: int, start: int, end: int) -> None:
         if end <= start:
@@ -332,6 +350,41 @@ class PagedReqTokensManager:
         self.req_token_count[req_idx] = new_total
         return True
 
+    def extend_batch_for_device(self, req_indices) -> Optional[int]:
+        """Host half of a device-side decode step: grow every request by one token, allocating a
+        page only where a page boundary is crossed, WITHOUT queueing per-token table writes (the
+        metadata kernel writes the device token table itself).  The host mirror of the token table
+        is kept exact with one vectorised write.  Returns ``None`` on success or the request id
+        whose extension failed (earlier requests of the batch stay extended, as with
+        ``extend_req`` in a loop)."""
+        ps = self.page_mgr.page_size
+        counts = self.req_token_count
+        n = len(req_indices)
+        rows = np.fromiter(req_indices, dtype=np.int64, count=n)
+        cur = np.fromiter((counts[r] for r in req_indices), dtype=np.int64, count=n)
+        failed = None
+        # the rare cases, in batch order: a row at its maximum length, or one that needs a page
+        special = np.flatnonzero((cur >= self.max_seq_len) | (cur // ps >= self._host_page_counts.numpy()[rows]))
+        for i in special.tolist():
+            req_idx = int(rows[i])
+            if cur[i] + 1 > self.max_seq_len:
+                failed = i
+                break
+            have = len(self.req_page_table[req_idx])
+            extra = self.page_mgr.alloc(ps)
+            if extra is None:
+                failed = i
+                break
+            self.req_page_table[req_idx] = torch.cat([self.req_page_table[req_idx], extra])
+            self._write_pages(req_idx, have)
+        if failed is not None:
+            rows, cur = rows[:failed], cur[:failed]
+        for r in rows.tolist():
+            counts[r] += 1
+        blocks, tokens = self._host_blocks.numpy(), self._host_tokens.numpy()
+        tokens[rows, cur] = blocks[rows, cur // ps] * ps + cur % ps
+        return None if failed is None else int(req_indices[failed])
+
     def get_token_indices(self, req_idx: int, num_tokens: Optional[int] = None) -> torch.Tensor:
         """Device view of the physical slots of a request's first ``num_tokens`` tokens."""
         if num_tokens is None:
@@ -343,6 +396,8 @@ class PagedReqTokensManager:
             self.page_mgr.free(self.req_page_table[req_idx])
             del self.req_page_table[req_idx]
             del self.req_token_count[req_idx]
+            self._host_page_counts[req_idx] = 0
+            self._dirty_counts = True
         self.req_active[req_idx] = False
         if req_idx not in self.free_req_indices:
             bisect.insort(self.free_req_indices, req_idx)

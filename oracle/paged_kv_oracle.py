@@ -253,3 +253,20 @@ def qk_norm_rope_append(xq, xkv, q_weight, k_weight, eps, cos, sin, select_index
     k = rotate_halves(head_rmsnorm(xk, k_weight, eps), cos, sin)
     kv_append(torch.cat([k, xv], dim=-2), select_index, kv_buffer)
     return q
+
+
+def decode_advance(seq_lens: torch.Tensor, block_table: torch.Tensor, page_size: int,
+                   req_ids: Optional[torch.Tensor] = None,
+                   token_table: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One decode step of batch metadata: the new token of sequence b sits at logical position
+    ``seq_lens[b]`` of table row ``req_ids[b]``; its slot is ``page * page_size + offset``
+    (executor/paged_attention.py:346-358 writes exactly this entry in ``extend_req``), the length
+    grows by one, and ``batch_metadata`` (:287-311) reports the new length and that slot.
+    ``seq_lens`` and ``token_table`` are updated in place; returns the int32 slots."""
+    rows = (req_ids if req_ids is not None else torch.arange(seq_lens.shape[0])).long()
+    pos = seq_lens.long()
+    slots = (block_table[rows, pos // page_size].long() * page_size + pos % page_size).to(torch.int32)
+    if token_table is not None:
+        token_table[rows, pos] = slots
+    seq_lens += 1
+    return slots

@@ -53,6 +53,12 @@ PROLOGUE_CASES = {
 }
 PROLOGUE_EPS = 1e-6
 
+# Decode-step metadata script: five prompts, one released (gap in the ids), batch rows out of order.
+METADATA_SCRIPT = {
+    "num_pages": 64, "page_size": 4, "max_requests": 8, "max_seq_len": 64,
+    "prompt_lengths": [5, 8, 3, 15, 1], "drop": 1, "batch_order": [3, 0, 4, 2], "steps": 21,
+}
+
 MHA_DECODE_CASES = {
     "decode_contiguous_mha": (3, 4, [50, 128, 77]),
 }

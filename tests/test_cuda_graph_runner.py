@@ -112,9 +112,11 @@ def test_failed_capture_falls_back_and_is_not_retried():
 
 
 @pytest.mark.gpu
-def test_paged_decode_step_replays_in_cuda_graph():
+@pytest.mark.parametrize("extend", ["extend_paged_requests", "extend_paged_requests_on_device"])
+def test_paged_decode_step_replays_in_cuda_graph(extend):
     """Two 'layers' of (append + paged decode) captured once, replayed over several steps while
-    the host managers keep extending the requests; every replay equals the eager result."""
+    the requests keep growing (metadata from the host, or advanced on the device); every replay
+    equals the eager result."""
     dev, kvh, heads, layers = "cuda:0", 2, 16, 2
     ex = PagedKVExecutor(layers, kvh, 128, 512, 8, 1024, page_size=16, device=dev)
     for buf in ex.kv_mem_manager.gpu_kv_buffer:
@@ -139,8 +141,8 @@ def test_paged_decode_step_replays_in_cuda_graph():
     xk = torch.empty(4, kvh, 128, dtype=torch.float16, device=dev)
     xv = torch.empty(4, kvh, 128, dtype=torch.float16, device=dev)
     inp = torch.zeros(4, 1, dtype=torch.long, device=dev)
-    for step in range(5):
-        ex.extend_paged_requests(ids)
+    for step in range(20):                                   # every row crosses a page boundary
+        getattr(ex, extend)(ids)
         xq.copy_(W.hash_normal_fp16(50 + step, (4, heads, 128), 1))
         xk.copy_(W.hash_normal_fp16(50 + step, (4, kvh, 128), 2))
         xv.copy_(W.hash_normal_fp16(50 + step, (4, kvh, 128), 3))
@@ -149,4 +151,6 @@ def test_paged_decode_step_replays_in_cuda_graph():
         torch.cuda.synchronize()
         # the bucketed length bound may split the page line differently from the exact one
         assert float((got.float() - want.float()).abs().max()) <= 2e-3, step
-    assert (runner.capture_count, runner.replay_count, runner.fallback_count) == (1, 5, 0)
+    assert (runner.capture_count, runner.replay_count, runner.fallback_count) == (1, 20, 0)
+    from llama_lite_npu_b200 import kernels
+    kernels.check_status(0)
