@@ -164,6 +164,19 @@ int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i
                           int32_t* status, void* stream);
 
 /*
+ * req_to_token_indexs[b_req_idx[i]][b_seq_len[i] - 1] = select_index[i] for i in [0, n).
+ * Replaces update_kv_index (lite_llama/kernels/update_kv_index.py:42-74, kernel :6-38), the
+ * token-table write of the non-paged decode path
+ * (lite_llama/executor/model_executor.py:958-967).  Strides in elements.  An index outside
+ * the table sets B200KV_DEV_BAD_LENGTH and skips that entry.  Bit-exact.
+ */
+int b200kv_update_kv_index(int32_t* req_to_token_indexs, int64_t row_stride, int64_t col_stride,
+                           int rows, int cols,
+                           const int32_t* b_req_idx, const void* b_seq_len, int seq_lens_i64,
+                           const int32_t* select_index, int n,
+                           int32_t* status, void* stream);
+
+/*
  * Bytes of scratch that b200kv_paged_decode needs for a batch of `batch`
  * sequences on the CURRENT device (split-KV partial outputs and their
  * log-sum-exp).  Depends on the device's SM count.  Returns 0 on bad input.

@@ -45,6 +45,11 @@ _SIGNATURES = {
          c_void_p, c_int64, c_int,                       # token table
          c_int, c_int, c_int64, c_void_p, c_void_p],
     ),
+    "b200kv_update_kv_index": (
+        c_int,
+        [c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+         c_void_p, c_void_p],
+    ),
     "b200kv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200kv_paged_decode": (
         c_int,

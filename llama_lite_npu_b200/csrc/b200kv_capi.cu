@@ -139,6 +139,15 @@ int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i
   return b200kv::decode_advance(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_update_kv_index(int32_t* req_to_token_indexs, int64_t row_stride, int64_t col_stride,
+                           int rows, int cols, const int32_t* b_req_idx, const void* b_seq_len,
+                           int seq_lens_i64, const int32_t* select_index, int n, int32_t* status,
+                           void* stream) {
+  return b200kv::update_kv_index(req_to_token_indexs, row_stride, col_stride, rows, cols, b_req_idx,
+                                 b_seq_len, seq_lens_i64, select_index, n, status,
+                                 static_cast<cudaStream_t>(stream));
+}
+
 size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
   return b200kv::decode_workspace_bytes(batch, q_heads, kv_heads, head_dim);
 }

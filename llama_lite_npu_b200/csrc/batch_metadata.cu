@@ -65,7 +65,57 @@ __global__ void __launch_bounds__(128) decode_advance_kernel(AdvanceParams p) {
     reinterpret_cast<int32_t*>(p.seq_lens)[b] = static_cast<int32_t>(pos + 1);
 }
 
+// table[req_ids[i]][seq_lens[i] - 1] = select_index[i]: the token-table write of the reference's
+// non-paged decode path (lite_llama/kernels/update_kv_index.py:6-38).
+struct IndexParams {
+  int32_t* table;
+  int64_t row_stride, col_stride;
+  int rows, cols;
+  const int32_t* req_ids;
+  const void* seq_lens;
+  int seq_lens_i64;
+  const int32_t* select_index;
+  int n;
+  int32_t* status;
+};
+
+__global__ void __launch_bounds__(128) update_kv_index_kernel(IndexParams p) {
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= p.n) return;
+  const int row = p.req_ids[i];
+  const int64_t col = load_len(p.seq_lens, p.seq_lens_i64, i) - 1;
+  if (row < 0 || row >= p.rows || col < 0 || col >= p.cols) {
+    set_status(p.status, B200KV_DEV_BAD_LENGTH);
+    return;
+  }
+  p.table[row * p.row_stride + col * p.col_stride] = p.select_index[i];
+}
+
 }  // namespace
+
+int update_kv_index(int32_t* table, int64_t row_stride, int64_t col_stride, int rows, int cols,
+                    const int32_t* req_ids, const void* seq_lens, int seq_lens_i64,
+                    const int32_t* select_index, int n, int32_t* status, cudaStream_t stream) {
+  if (n < 0 || rows <= 0 || cols <= 0) return B200KV_EINVAL;
+  if (n == 0) return B200KV_OK;
+  if (!table || !req_ids || !seq_lens || !select_index) return B200KV_EINVAL;
+  IndexParams p{table, row_stride, col_stride, rows, cols, req_ids, seq_lens, seq_lens_i64,
+                select_index, n, status};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>((n + 127) / 128));
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, update_kv_index_kernel, p);
+  if (e != cudaSuccess) return record_cuda_error(e);
+  return check_launch();
+}
 
 int decode_advance(const AdvanceArgs& a, cudaStream_t stream) {
   if (a.batch < 0 || a.table_rows <= 0 || a.table_pages <= 0 || a.page_size <= 0 || a.pool_pages <= 0)

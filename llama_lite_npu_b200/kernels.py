@@ -211,6 +211,34 @@ def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: tor
 
 
 @torch.no_grad()
+def update_kv_index(req_to_token_indexs: torch.Tensor, b_req_idx: torch.Tensor, b_seq_len: torch.Tensor,
+                    select_index: torch.Tensor) -> None:
+    """``req_to_token_indexs[b_req_idx[i], b_seq_len[i] - 1] = select_index[i]`` on the device.
+
+    Same signature as the reference operator (``lite_llama/kernels/update_kv_index.py:42-74``)."""
+    dev = _device_index(req_to_token_indexs)
+    _require(req_to_token_indexs.dtype == torch.int32 and req_to_token_indexs.dim() == 2,
+             "req_to_token_indexs must be a 2-D int32 tensor")
+    _, i64 = _lens_arg(b_seq_len, "b_seq_len")
+    n = b_seq_len.shape[0]
+    _require(b_req_idx.shape[0] == n and select_index.shape[0] == n,
+             "b_req_idx, b_seq_len and select_index must have the same length")
+    for t, name in ((b_req_idx, "b_req_idx"), (select_index, "select_index")):
+        _require(t.dtype == torch.int32 and t.dim() == 1 and t.is_contiguous(),
+                 f"{name} must be a contiguous 1-D int32 tensor")
+    if n == 0:
+        return
+    t = req_to_token_indexs
+    with _on_device(dev):
+        rc = _lib.lib().b200kv_update_kv_index(
+            t.data_ptr(), t.stride(0), t.stride(1), t.shape[0], t.shape[1], b_req_idx.data_ptr(),
+            b_seq_len.data_ptr(), i64, select_index.data_ptr(), n, status_tensor(dev).data_ptr(),
+            _stream(dev))
+    _lib.check(rc)
+    _after_call(dev)
+
+
+@torch.no_grad()
 def advance_decode_metadata(b_seq_len: torch.Tensor, cur_select_index: torch.Tensor,
                             b_req_block_table: torch.Tensor, page_size: int, num_pages: int, *,
                             b_req_idx: Optional[torch.Tensor] = None,

@@ -270,3 +270,10 @@ def decode_advance(seq_lens: torch.Tensor, block_table: torch.Tensor, page_size:
         token_table[rows, pos] = slots
     seq_lens += 1
     return slots
+
+
+def update_kv_index(req_to_token_indexs, b_req_idx, b_seq_len, select_index) -> None:
+    """``req_to_token_indexs[b_req_idx[i], b_seq_len[i] - 1] = select_index[i]`` in place
+    (kernels/update_kv_index.py:16-36; the reference holds no torch statement or fixture for it,
+    so this restates the kernel body)."""
+    req_to_token_indexs[b_req_idx.long(), b_seq_len.long() - 1] = select_index.to(req_to_token_indexs.dtype)

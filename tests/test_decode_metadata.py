@@ -140,3 +140,28 @@ def test_executor_device_extend_equals_host_extend(built_lib):
     assert torch.equal(host.atten_info.b_seq_len, devp.atten_info.b_seq_len)
     from llama_lite_npu_b200 import kernels
     kernels.check_status(0)
+
+
+@pytest.mark.gpu
+def test_update_kv_index_matches_statement(built_lib):
+    from llama_lite_npu_b200 import kernels, workloads as W
+
+    dev = "cuda:0"
+    table = torch.from_numpy(W.hash_randint(4, 16 * 300, 0, 1 << 20, 1).astype("int32")).view(16, 300)
+    req = torch.from_numpy(W.hash_permutation(4, 16, 2)[:11].astype("int32"))
+    lens = torch.from_numpy(W.hash_randint(4, 11, 1, 301, 3))
+    sel = torch.from_numpy(W.hash_randint(4, 11, 0, 1 << 20, 4).astype("int32"))
+    for dtype in (torch.int32, torch.int64):
+        want = table.clone()
+        O.update_kv_index(want, req, lens.to(dtype), sel)
+        got = table.to(dev)
+        kernels.update_kv_index(got, req.to(dev), lens.to(dtype).to(dev), sel.to(dev))
+        assert torch.equal(got.cpu(), want)
+    view = table.to(dev).t().contiguous().t()                       # column-major strides
+    kernels.update_kv_index(view, req.to(dev), lens.to(dev), sel.to(dev))
+    assert torch.equal(view.cpu(), want)
+    kernels.check_status(0)
+    kernels.update_kv_index(got, req[:1].to(dev), torch.tensor([0], device=dev), sel[:1].to(dev))
+    with pytest.raises(RuntimeError, match="length"):
+        kernels.check_status(0)
+    assert torch.equal(got.cpu(), want)
