@@ -232,8 +232,9 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const uint32_t bar_sfull = bar_empty + 8 * kSlots;        // [kGroups] S_g of a tile is in TMEM
   const uint32_t bar_pfull = bar_sfull + 8 * kGroups;       // [kGroups] P_g of a tile is in shared memory
   const uint32_t bar_pvfull = bar_pfull + 8 * kGroups;      // [kGroups] O_g += P_g V of a tile completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_pvfull + 8 * kGroups - sm_q));
-  static_assert(8 + 2 * 8 * kSlots + 3 * 8 * kGroups + 8 <= kBarBytes, "barrier area too small");
+  const uint32_t bar_sfree = bar_pvfull + 8 * kGroups;      // [kGroups] S_g of a tile is in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_sfree + 8 * kGroups - sm_q));
+  static_assert(8 + 2 * 8 * kSlots + 4 * 8 * kGroups + 8 <= kBarBytes, "barrier area too small");
   if ((sm_q & 1023u) != 0) {  // swizzled boxes and UMMA descriptors assume 1024-byte alignment
     set_status(p.status, B200KV_DEV_BAD_PAGE);
     return;
@@ -249,6 +250,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       mbar_init(bar_sfull + 8 * g, 1);
       mbar_init(bar_pfull + 8 * g, kGroupWarps * 32);
       mbar_init(bar_pvfull + 8 * g, 1);
+      mbar_init(bar_sfree + 8 * g, kGroupWarps * 32);
     }
     fence_barrier_init();
   }
@@ -263,6 +265,11 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Ring order: K runs one tile ahead of V, K_0 K_1 V_0 K_2 V_1 ... K_{T-1} V_{T-2} V_{T-1}, which is
+  // also the order in which the tensor core finishes with the tiles (S of tile j+1 is issued
+  // before P V of tile j).  Item n lives in slot n % kSlots.
+  auto pos_k = [](int t) { return t == 0 ? 0 : 2 * t - 1; };
+  auto pos_v = [n_tiles](int t) { return t == n_tiles - 1 ? 2 * n_tiles - 1 : 2 * t + 2; };
   cudaGridDependencySynchronize();  // q and the pool belong to earlier kernels until here
   cudaTriggerProgrammaticLaunchCompletion();
 
@@ -296,12 +303,22 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       if (lane >= 16 || j >= n_tiles || lp >= n_pages || p.table_kind == B200KV_TABLE_DENSE) return 0;
       return __ldg(trow + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
     };
-    int32_t id_cur = fetch_id(0);
-    int32_t id_next = fetch_id(1);
+    // Item n of the ring order above: which tile, and K or V.
+    auto item_tile = [n_tiles](int n, bool& is_v) {
+      if (n == 0) { is_v = false; return 0; }
+      if (n == 2 * n_tiles - 1) { is_v = true; return n_tiles - 1; }
+      is_v = (n & 1) == 0;
+      return is_v ? (n - 2) / 2 : (n + 1) / 2;
+    };
+    bool v_cur;
+    int t_cur = item_tile(0, v_cur);
+    int32_t id_cur = fetch_id(t_cur);
     bool ok = true;
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      const int32_t id_after = fetch_id(j + 2);   // in flight while this tile is issued
-      const int64_t page0 = static_cast<int64_t>(j) * kTilePages;
+    for (int n = 0; ok && n < 2 * n_tiles; ++n) {
+      bool v_next = false;
+      const int t_next = n + 1 < 2 * n_tiles ? item_tile(n + 1, v_next) : n_tiles;
+      const int32_t id_next = fetch_id(t_next);   // in flight while this item is issued
+      const int64_t page0 = static_cast<int64_t>(t_cur) * kTilePages;
       const int np = static_cast<int>(n_pages - page0 < kTilePages ? n_pages - page0 : kTilePages);
       const int64_t lp = page0 + my_page;
       int64_t slot;
@@ -313,23 +330,20 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         slot = 0;  // never dereference a bad entry: report it and read page 0 instead
       }
       const uint32_t dst_off = my_half * (kTileBytes / 2) + my_page * kHalfPage;
-#pragma unroll
-      for (int kv = 0; kv < 2; ++kv) {               // item 2j = K_j, item 2j+1 = V_j
-        const int item = 2 * j + kv;
-        const int sl = item % kSlots;
-        if (item >= kSlots && !mbar_wait_bounded(bar_empty + 8 * sl, ((item / kSlots) - 1) & 1)) {
-          set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-          ok = false;
-          break;
-        }
-        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * sl, np * 2 * kHalfPage);
-        __syncwarp();
-        if (lane < 2 * np)
-          tma_load_3d(sm_ring + sl * kTileBytes + dst_off, kv ? &vmap : &kmap, bar_full + 8 * sl, my_half * 64,
-                      kv_head, static_cast<int>(slot), policy);
+      const int sl = n % kSlots;
+      if (n >= kSlots && !mbar_wait_bounded(bar_empty + 8 * sl, ((n / kSlots) - 1) & 1)) {
+        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+        ok = false;
+        break;
       }
+      if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * sl, np * 2 * kHalfPage);
+      __syncwarp();
+      if (lane < 2 * np)
+        tma_load_3d(sm_ring + sl * kTileBytes + dst_off, v_cur ? &vmap : &kmap, bar_full + 8 * sl, my_half * 64,
+                    kv_head, static_cast<int>(slot), policy);
+      t_cur = t_next;
+      v_cur = v_next;
       id_cur = id_next;
-      id_next = id_after;
     }
   } else if (warp == kMmaWarp) {
     // ============================== MMA issuer ==============================================
@@ -348,7 +362,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       constexpr uint64_t kChunkStep = (kTileBytes / 2) >> 4;   // second 64-wide chunk of an operand tile
 
       auto issue_s = [&](int g, int j) {            // S_g = Q_g K_j^T : 8 x (M128 N128 K16)
-        const uint64_t kd = dk_base + static_cast<uint64_t>((2 * j) % kSlots) * kSlotStep;
+        const uint64_t kd = dk_base + static_cast<uint64_t>(pos_k(j) % kSlots) * kSlotStep;
         const uint64_t qd = g ? dq1 : dq0;
         const uint32_t d_s = tmem_base + kTmemS + g * kBN;
         tc_fence_after();
@@ -361,7 +375,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         umma_commit(bar_sfull + 8 * g);
       };
       auto issue_pv = [&](int g, int j) {           // O_g += P_g V_j : 8 x (M128 N128 K16)
-        const uint64_t vd = dv_base + static_cast<uint64_t>((2 * j + 1) % kSlots) * kSlotStep;
+        const uint64_t vd = dv_base + static_cast<uint64_t>(pos_v(j) % kSlots) * kSlotStep;
         const uint64_t pd = g ? dp1 : dp0;
         const uint32_t d_o = tmem_base + kTmemO + g * kD;
         tc_fence_after();
@@ -375,28 +389,33 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         umma_commit(bar_pvfull + 8 * g);
       };
       const int ng = active1 ? 2 : 1;
-      // Tensor-core order: S0_0 S1_0 | PV0_0 S0_1 | PV1_0 S1_1 | PV0_1 S0_2 | ...  A tile's next S is
-      // issued right behind its P V, so one tile is in its softmax while the other's MMAs run.
+      // Tensor-core order: S0_0 S1_0 | S0_1 S1_1 PV0_0 PV1_0 | S0_2 S1_2 PV0_1 PV1_1 | ...  The S of
+      // tile j+1 is issued as soon as the softmax group holds S of tile j in registers, so it runs
+      // under that softmax and the group does not wait for its next S.
       if (ok) ok = mbar_wait_bounded(bar_full + 8 * 0, 0);
       if (ok) {
         for (int g = 0; g < ng; ++g) issue_s(g, 0);
         umma_commit(bar_empty + 8 * 0);                     // K_0: both S issued
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        const int kslot_next = (2 * j + 2) % kSlots, vslot = (2 * j + 1) % kSlots;
-        const bool more = j + 1 < n_tiles;
-        for (int g = 0; g < ng; ++g) {
-          if (!mbar_wait_bounded(bar_pfull + 8 * g, j & 1)) { ok = false; break; }
-          if (g == 0 && !mbar_wait_bounded(bar_full + 8 * vslot, ((2 * j + 1) / kSlots) & 1)) { ok = false; break; }
-          issue_pv(g, j);
-          if (more) {
-            if (g == 0 && !mbar_wait_bounded(bar_full + 8 * kslot_next, ((2 * j + 2) / kSlots) & 1)) { ok = false; break; }
+        if (j + 1 < n_tiles) {
+          const int pk = pos_k(j + 1);
+          if (!mbar_wait_bounded(bar_full + 8 * (pk % kSlots), (pk / kSlots) & 1)) { ok = false; break; }
+          for (int g = 0; ok && g < ng; ++g) {
+            if (!mbar_wait_bounded(bar_sfree + 8 * g, j & 1)) { ok = false; break; }
             issue_s(g, j + 1);
           }
+          if (!ok) break;
+          umma_commit(bar_empty + 8 * (pk % kSlots));       // K_{j+1}: both S issued
+        }
+        const int pv = pos_v(j);
+        if (!mbar_wait_bounded(bar_full + 8 * (pv % kSlots), (pv / kSlots) & 1)) { ok = false; break; }
+        for (int g = 0; ok && g < ng; ++g) {
+          if (!mbar_wait_bounded(bar_pfull + 8 * g, j & 1)) { ok = false; break; }
+          issue_pv(g, j);
         }
         if (!ok) break;
-        umma_commit(bar_empty + 8 * vslot);                 // V_j: both P V issued
-        if (more) umma_commit(bar_empty + 8 * kslot_next);  // K_{j+1}: both S issued
+        umma_commit(bar_empty + 8 * (pv % kSlots));         // V_j: both P V issued
       }
       if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
     }
@@ -433,16 +452,19 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       tmem_ld32(tmem_s + 96, sr[3]);
       tmem_ld_wait();
       tc_fence_before();
+      mbar_arrive(bar_sfree + 8 * g);                      // S_g may be overwritten by the next tile's S
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < kBN; ++c)
           if (c > lim) sr[c >> 5][c & 31] = 0xff800000u;   // -inf
       }
       // Row maximum of the RAW scores (the scale is positive), two new elements per instruction.
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four independent chains
 #pragma unroll
       for (int c = 0; c < kBN; c += 2)
-        mx = max3(mx, __uint_as_float(sr[c >> 5][c & 31]), __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+        mx4[(c >> 1) & 3] = max3(mx4[(c >> 1) & 3], __uint_as_float(sr[c >> 5][c & 31]),
+                                 __uint_as_float(sr[(c + 1) >> 5][(c + 1) & 31]));
+      float mx = fmaxf(max3(mx4[0], mx4[1], mx4[2]), mx4[3]);
       mx *= p.scale_log2;
       // P_g and O_g are free once the P V MMAs of tile j-1 have completed (they were issued
       // before this tile's S, so this wait is normally already satisfied).
@@ -504,12 +526,12 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         unpack_f32x2(rs2[1], b0, b1);
         l_run += (a0 + a1) + (b0 + b1);
       }
-      if (g == 0 && j == n_tiles - 1) {
+      if (j == n_tiles - 1) {
         // Keys past kv_len in the last tile were either not loaded or lie in never-written pool
-        // slots; their P is 0 but 0 * NaN would still poison the row, so zero those V rows.  Group
-        // 0 does it before publishing P_0; the MMA warp waits for P_0 before issuing either
-        // tile's P V, so both tiles read the cleaned V.
-        const int item = 2 * j + 1;
+        // slots; their P is 0 but 0 * NaN would still poison the row, so zero those V rows.  Each
+        // group does the whole clean-up before publishing its own P, which is what its own P V
+        // waits for; the two groups write the same zeros.
+        const int item = pos_v(j);
         const int sl = item % kSlots;
         const int valid = static_cast<int>(kv_len - key0);
         if (valid < kBN) {
