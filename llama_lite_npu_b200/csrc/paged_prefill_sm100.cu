@@ -11,18 +11,20 @@
 // so K/V cross L2 -> shared memory once for both and the tensor core always has the other tile's
 // MMAs to run while one tile is in its softmax.  Ten warps, one CTA per SM:
 //   warp 8  producer : TMA (cp.async.bulk.tensor) of both Q tiles once, then of the K and V pages
-//                      of each 128-key tile into a 3-slot ring of 32 KB slots in which K and V
-//                      tiles alternate (K_0 V_0 K_1 V_1 ...); pages come through the block/token
-//                      table (entries fetched two tiles ahead), each page of one head is two
-//                      16-row x 128-byte swizzled boxes, one per lane;
+//                      of each 128-key tile into a 3-slot ring of 32 KB slots in which K runs one
+//                      tile ahead of V (K_0 K_1 V_0 K_2 V_1 ...), the order in which the tensor
+//                      core finishes with them; pages come through the block/token table (entry
+//                      fetched one item ahead), each page of one head is two 16-row x 128-byte
+//                      swizzled boxes, one per lane;
 //   warp 9  MMA      : one lane issues tcgen05.mma.cta_group::1.kind::f16, always as M128 N128 K16
 //                      (the per-instruction cost of tcgen05.mma is nearly flat in N, so small-N
 //                      instructions waste the tensor pipe): S_g = Q_g K^T (8 instructions) into
-//                      TMEM and, once softmax group g has published P_g, O_g += P_g V (8
-//                      instructions) followed at once by that tile's next S; descriptors are built
-//                      once and only their address field advances; tcgen05.commit signals mbarriers;
+//                      TMEM, for key tile j+1 as soon as softmax group g holds S_g of tile j in
+//                      registers (so it runs under that softmax), and O_g += P_g V (8
+//                      instructions) once the group has published P_g; descriptors are built once
+//                      and only their address field advances; tcgen05.commit signals mbarriers;
 //   warps 0-3 / 4-7  : softmax group 0 / 1: thread i owns query row i = TMEM lane i of its tile:
-//                      tcgen05.ld of its S row in two 64-column halves, causal mask on diagonal
+//                      tcgen05.ld of its whole 128-column S row, causal mask on diagonal
 //                      tiles only, online softmax in the log2 domain (3-input max, packed f32x2
 //                      FFMA/ADD, exp2), P rounded to fp16 and written to shared memory in the UMMA
 //                      K-major 128-byte-swizzled layout; O accumulates in TMEM and is rescaled only
@@ -397,24 +399,38 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         for (int g = 0; g < ng; ++g) issue_s(g, 0);
         umma_commit(bar_empty + 8 * 0);                     // K_0: both S issued
       }
+      // This thread paces the CTA (the tensor core idles whenever it is not issuing), and a barrier
+      // test costs it a few hundred cycles even when the phase is long complete.  So the three
+      // barriers a step depends on are tested together (independent instructions, one latency)
+      // and only the ones that were not ready are waited for.
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (j + 1 < n_tiles) {
           const int pk = pos_k(j + 1);
-          if (!mbar_wait_bounded(bar_full + 8 * (pk % kSlots), (pk / kSlots) & 1)) { ok = false; break; }
-          for (int g = 0; ok && g < ng; ++g) {
-            if (!mbar_wait_bounded(bar_sfree + 8 * g, j & 1)) { ok = false; break; }
-            issue_s(g, j + 1);
+          const uint32_t b_k = bar_full + 8 * (pk % kSlots), par_k = (pk / kSlots) & 1;
+          const bool r_k = mbar_test_wait(b_k, par_k);
+          const bool r_0 = mbar_test_wait(bar_sfree, j & 1);
+          const bool r_1 = ng > 1 ? mbar_test_wait(bar_sfree + 8, j & 1) : true;
+          if (!r_k && !mbar_wait_bounded(b_k, par_k)) { ok = false; break; }
+          if (!r_0 && !mbar_wait_bounded(bar_sfree, j & 1)) { ok = false; break; }
+          issue_s(0, j + 1);
+          if (ng > 1) {
+            if (!r_1 && !mbar_wait_bounded(bar_sfree + 8, j & 1)) { ok = false; break; }
+            issue_s(1, j + 1);
           }
-          if (!ok) break;
           umma_commit(bar_empty + 8 * (pk % kSlots));       // K_{j+1}: both S issued
         }
         const int pv = pos_v(j);
-        if (!mbar_wait_bounded(bar_full + 8 * (pv % kSlots), (pv / kSlots) & 1)) { ok = false; break; }
-        for (int g = 0; ok && g < ng; ++g) {
-          if (!mbar_wait_bounded(bar_pfull + 8 * g, j & 1)) { ok = false; break; }
-          issue_pv(g, j);
+        const uint32_t b_v = bar_full + 8 * (pv % kSlots), par_v = (pv / kSlots) & 1;
+        const bool r_v = mbar_test_wait(b_v, par_v);
+        const bool r_0 = mbar_test_wait(bar_pfull, j & 1);
+        const bool r_1 = ng > 1 ? mbar_test_wait(bar_pfull + 8, j & 1) : true;
+        if (!r_v && !mbar_wait_bounded(b_v, par_v)) { ok = false; break; }
+        if (!r_0 && !mbar_wait_bounded(bar_pfull, j & 1)) { ok = false; break; }
+        issue_pv(0, j);
+        if (ng > 1) {
+          if (!r_1 && !mbar_wait_bounded(bar_pfull + 8, j & 1)) { ok = false; break; }
+          issue_pv(1, j);
         }
-        if (!ok) break;
         umma_commit(bar_empty + 8 * (pv % kSlots));         // V_j: both P V issued
       }
       if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
