@@ -58,8 +58,11 @@ constexpr int kStageBytes = 2 * kTileBytes;
 #endif
 constexpr int kCtasPerSm = B200KV_DECODE_CTAS_PER_SM;
 constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
-constexpr int kMinPagesPerTeam = 8;
-constexpr int kCombineThreads = 128;
+#ifndef B200KV_DECODE_MIN_PAGES
+#define B200KV_DECODE_MIN_PAGES 8
+#endif
+constexpr int kMinPagesPerTeam = B200KV_DECODE_MIN_PAGES;   // a team is not worth launching for fewer pages
+constexpr int kCombineThreads = 256;   // at most; the launch picks 128 or 256
 
 struct DecodeParams {
   const __half* q;
@@ -580,9 +583,10 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
 
 // Merge the split partials of each sequence: out = sum_p 2^(lse_p - M) o_p / sum_p 2^(lse_p - M)
 // (stage 2 of the reference, lite_llama/kernels/flashdecoding.py:199-267).  One CTA per
-// (sequence, KV head), one warp per query head of the group at a time; lanes hold the pieces'
-// log-sum-exp values and reduce them with warp shuffles, then every lane accumulates four
-// output columns.  Launched with programmatic stream serialisation: everything before
+// (sequence, KV head), one warp per query head of the group; every lane accumulates four output
+// columns over the pieces.  Up to four pieces: all loads issued together, one round trip.  More:
+// lanes hold the pieces' log-sum-exp values, maximum and weight sum are warp-shuffle reductions,
+// and the partial outputs are loaded eight pieces at a time.  Launched with programmatic stream serialisation: everything before
 // pdl_wait_then_trigger() (recomputing which teams touched this sequence) overlaps the tail
 // of the split kernel.
 template <int ROWS>
@@ -595,7 +599,8 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   const int warp = tid >> 5;
 
   long long before = 0, total = 0;
-  for (int i = tid; i < p.batch; i += kCombineThreads) {
+  const int nthreads = blockDim.x, nwarps = nthreads >> 5;
+  for (int i = tid; i < p.batch; i += nthreads) {
     const int np = pages_of(seq_len_checked(p, i));
     total += np;
     if (i < b) before += np;
@@ -611,8 +616,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   }
   __syncthreads();
   before = total = 0;
-#pragma unroll
-  for (int w = 0; w < kCombineThreads / 32; ++w) {
+  for (int w = 0; w < nwarps; ++w) {
     before += red[0][w];
     total += red[1][w];
   }
@@ -620,7 +624,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   const int len = seq_len_checked(p, b);
   if (len == 0) {  // no keys: the output rows are defined as zero (nobody else writes them)
     pdl_wait_then_trigger();
-    for (int i = tid; i < p.group * kD; i += kCombineThreads) {
+    for (int i = tid; i < p.group * kD; i += nthreads) {
       const int g = i / kD;
       p.out[static_cast<int64_t>(b) * p.out_stride_b +
             (static_cast<int64_t>(kvh) * p.group + g) * p.out_stride_h + (i - g * kD)] =
@@ -637,7 +641,7 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
 
   pdl_wait_then_trigger();  // partials of the split kernel are visible from here on
 
-  for (int g = warp; g < p.group; g += kCombineThreads / 32) {
+  for (int g = warp; g < p.group; g += nwarps) {
     const int hq = kvh * p.group + g;
     if (npieces <= 4) {
       // Common case: issue the loads of every piece's log-sum-exp AND output together, so the
@@ -672,6 +676,10 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
                                 static_cast<int64_t>(hq) * p.out_stride_h + lane * 4) = pk4;
       continue;
     }
+    // More pieces (short shards of a long batch: few KV heads per GPU, many teams).  Lane i holds
+    // the log-sum-exp of piece p0 + i: the maximum and the weight sum are warp-shuffle reductions,
+    // and the weights reach the accumulating lanes by shuffle; the partial outputs are loaded
+    // eight pieces at a time, every load of a chunk issued before any arithmetic.
     float M = -INFINITY;
     for (int p0 = 0; p0 < npieces; p0 += 32) {
       const int pc = p0 + lane;
@@ -689,19 +697,27 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
       float w = 0.f;
       if (pc < npieces) {
         const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + kvh;
-        w = fast_exp2(p.part_lse[slot * ROWS + g] - M);
+        w = fast_exp2(p.part_lse[slot * ROWS + g] - M);   // second read of the same line: a cache hit
       }
       wsum += w;
       const int cnt = min(32, npieces - p0);
-      for (int j = 0; j < cnt; ++j) {
-        const float wj = __shfl_sync(0xffffffffu, w, j);
-        const int64_t slot = (static_cast<int64_t>(t_first + p0 + j) + b) * p.kv_heads + kvh;
-        const float4 ov =
-            *reinterpret_cast<const float4*>(p.part_o + (slot * ROWS + g) * kD + lane * 4);
-        acc.x += wj * ov.x;
-        acc.y += wj * ov.y;
-        acc.z += wj * ov.z;
-        acc.w += wj * ov.w;
+      for (int j0 = 0; j0 < cnt; j0 += 8) {
+        float4 ov[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int64_t slot =
+              (static_cast<int64_t>(t_first + p0 + min(j0 + j, cnt - 1)) + b) * p.kv_heads + kvh;
+          ov[j] = *reinterpret_cast<const float4*>(p.part_o + (slot * ROWS + g) * kD + lane * 4);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float wj = __shfl_sync(0xffffffffu, w, (j0 + j) & 31);
+          if (j0 + j >= cnt) wj = 0.f;
+          acc.x += wj * ov[j].x;
+          acc.y += wj * ov[j].y;
+          acc.z += wj * ov[j].z;
+          acc.w += wj * ov[j].w;
+        }
       }
     }
 #pragma unroll
@@ -753,7 +769,9 @@ int launch_decode(const DecodeParams& p, const CUtensorMap& kmap, const CUtensor
   int rc = check_launch();
   if (rc != B200KV_OK) return rc;
   cfg.gridDim = dim3(static_cast<unsigned>(p.batch * p.kv_heads));
-  cfg.blockDim = dim3(kCombineThreads);
+  // Few (sequence, KV head) CTAs (a shard with one or two KV heads): give each query head of the
+  // group its own warp; many CTAs: four warps keep the kernel's prologue short.
+  cfg.blockDim = dim3(p.batch * p.kv_heads < 128 ? kCombineThreads : kCombineThreads / 2);
   cfg.dynamicSmemBytes = 0;
   e = cudaLaunchKernelEx(&cfg, decode_combine_kernel<ROWS>, p);
   if (e != cudaSuccess) return record_cuda_error(e);
