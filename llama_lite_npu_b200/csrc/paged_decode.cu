@@ -58,6 +58,9 @@ constexpr int kStageBytes = 2 * kTileBytes;
 #endif
 constexpr int kCtasPerSm = B200KV_DECODE_CTAS_PER_SM;
 constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
+#ifndef B200KV_DECODE_L2_PREFETCH
+#define B200KV_DECODE_L2_PREFETCH 2   // tiles prefetched into L2 before the dependency wait (<= kLead)
+#endif
 #ifndef B200KV_DECODE_MIN_PAGES
 #define B200KV_DECODE_MIN_PAGES 8
 #endif
@@ -346,10 +349,27 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     Fetch fq[kLead];
 #pragma unroll
     for (int i = 0; i < kLead; ++i) fetch_next(p, prod, fq[i]);
-    pdl_wait_then_trigger();  // the pool may have been written by the previous kernel
     const int my_page = lane >> 2;
     const int my_part = lane & 3;
     const CUtensorMap* my_map = (my_part & 2) ? &vmap : &kmap;
+#if B200KV_DECODE_L2_PREFETCH > 0
+    // Pull the first tiles towards L2 while the previous kernel is still finishing: L2 is the
+    // point of coherence, so rows that kernel writes afterwards are still seen by the real loads.
+#pragma unroll
+    for (int i = 0; i < B200KV_DECODE_L2_PREFETCH; ++i) {
+      const Fetch& f = fq[i];
+      if (lane < 4 * f.npages) {
+        int32_t id = f.id[0];
+#pragma unroll
+        for (int k = 1; k < kTilePages; ++k) id = (my_page == k) ? f.id[k] : id;
+        const int64_t slot = (p.table_kind == B200KV_TABLE_BLOCK) ? static_cast<int64_t>(id) * kPS
+                                                                  : static_cast<int64_t>(id);
+        if (slot >= 0 && slot + kPS <= p.pool_tokens)
+          tma_prefetch_l2_3d(my_map, (my_part & 1) * 64, head, static_cast<int>(slot));
+      }
+    }
+#endif
+    pdl_wait_then_trigger();  // the pool may have been written by the previous kernel
     const uint32_t my_off = my_page * kPageBytes + (my_part & 1) * (kPageBytes / 2) +
                             ((my_part & 2) ? kTileBytes : 0);
     for (int it = 0;; ++it) {
