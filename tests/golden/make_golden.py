@@ -2,7 +2,7 @@
 
 Usage (only where the reference checkout is available; it is not needed to run the tests):
 
-    python tests/golden/make_golden.py [--reference /path/to/llama_lite_npu]
+    python tests/golden/make_golden.py --reference /path/to/llama_lite_npu
 
 The reference modules are imported by file path (the package itself needs an NPU
 runtime), exactly as the reference's own tests do.  Inputs come from the bit-reproducible
@@ -57,7 +57,7 @@ from golden_cases import (  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     args = ap.parse_args()
     ref = Path(args.reference)
     chunk = load(ref, "ref_paged_chunk_fa", "lite_llama/kernels/paged_chunk_flashattention.py")

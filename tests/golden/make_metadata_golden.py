@@ -1,7 +1,7 @@
 """Generate ``decode_metadata_golden.json`` by driving the reference's own page-pool classes
 (lite_llama/executor/paged_attention.py) through decode steps on the CPU:
 
-    python tests/golden/make_metadata_golden.py [--reference /path/to/llama_lite_npu]
+    python tests/golden/make_metadata_golden.py --reference /path/to/llama_lite_npu
 
 For a batch with a gap in its request ids and out-of-order rows, every step calls
 ``extend_req(r, 1)`` per request and then ``batch_metadata`` exactly as the reference's executor
@@ -28,7 +28,7 @@ from golden_cases import METADATA_SCRIPT  # noqa: E402
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     ref = Path(ap.parse_args().reference)
     paged = load(ref, "ref_paged_attention", "lite_llama/executor/paged_attention.py")
     sc = METADATA_SCRIPT

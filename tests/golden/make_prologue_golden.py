@@ -5,7 +5,7 @@ attention prologue on the seeded inputs of ``tests/golden_cases.py``:
 * ``torch_rotary_emb``    tests/kernels/test_rope_forward.py:150-170  (the check of its rope kernel)
 * the scatter statement   lite_llama/kernels/update_kv_buffer.py:104-105
 
-    python tests/golden/make_prologue_golden.py [--reference /path/to/llama_lite_npu]
+    python tests/golden/make_prologue_golden.py --reference /path/to/llama_lite_npu
 
 Both statements run in fp16 on the CPU (every operation rounded to fp16), so they agree with the
 reference's kernels only to the tolerance the reference's own tests use (1e-3 absolute + relative
@@ -34,7 +34,7 @@ from golden_cases import PROLOGUE_CASES, PROLOGUE_EPS, build_prologue  # noqa: E
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project")
     ref = Path(ap.parse_args().reference)
     # skip_rmsnorm.py imports its sibling ``.utils``: give it a bare parent package whose path is
     # the reference's kernels folder (the folder's own __init__ needs the NPU runtime).

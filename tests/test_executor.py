@@ -150,3 +150,36 @@ def test_serving_scenario_on_gpu_matches_oracle():
             want = oracle_attend(xq, layer, list(batch), [0, 1, 2], [n - 1 for n in lens], [1, 1, 1])
             check(got, want)
     ex.release_paged_request_ids(batch)
+
+
+@pytest.mark.gpu
+def test_steady_decode_step_never_synchronises_with_the_host():
+    """The reference pins 'no device -> host conversion in the decode step' with a source-text
+    check (tests/test_decode_p0.py:272-289).  Here the property itself is checked: with torch's
+    synchronisation debug mode set to raise, a steady decode step (metadata advanced on the
+    device, append + paged decode, and the fused-prologue form) must run to completion, page
+    boundaries included."""
+    dev = "cuda:0"
+    ex = PagedKVExecutor(1, 2, 128, 128, 8, 512, page_size=16, device=dev)
+    ids = ex.reserve_paged_requests([30, 47, 5])
+    ex.extend_paged_requests(ids)                              # host path once: activates the batch
+    xq = torch.zeros(3, 8, 128, dtype=torch.float16, device=dev)
+    xk = torch.zeros(3, 2, 128, dtype=torch.float16, device=dev)
+    xkv = torch.zeros(3, 2 * 2 * 128, dtype=torch.float16, device=dev)
+    w = torch.ones(128, dtype=torch.float16, device=dev)
+    cos = torch.ones(3, 128, dtype=torch.float16, device=dev)
+    ex.token_forward(xq, xk, xk, 0, SCALE)                     # warm-up: workspace, status word
+    ex.fused_token_forward(xq, xkv, w, w, 1e-6, cos, cos, 0, SCALE)
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        for _ in range(20):
+            ex.extend_paged_requests_on_device(ids)
+            ex.token_forward(xq, xk, xk, 0, SCALE)
+            ex.fused_token_forward(xq, xkv, w, w, 1e-6, cos, cos, 0, SCALE)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    from llama_lite_npu_b200 import kernels
+    kernels.check_status(0)
+    assert ex.req_tokens_manager.req_token_count[ids[0]] == 30 + 1 + 20
