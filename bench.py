@@ -222,7 +222,7 @@ def run_b200(args, cfg_full):
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device(dev))
-    cfg = W.shard_kv_heads(cfg_full, world, rank) if world > 1 else cfg_full
+    cfg, parallelism = W.shard_config(cfg_full, world, rank)
     scale = 1.0 / math.sqrt(cfg.head_dim)
     kvh = cfg.kv_heads
 
@@ -386,7 +386,7 @@ def run_b200(args, cfg_full):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
-            "config": dict(workload_config(cfg_full, world, layers),
+            "config": dict(workload_config(cfg_full, world, layers), parallelism=parallelism,
                            **({"step_prologue": "fused QK-RMSNorm + rotary embedding + KV append"}
                               if args.prologue else {})),
             "bytes_per_step": job_bytes,

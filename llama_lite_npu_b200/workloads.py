@@ -121,6 +121,29 @@ def shard_kv_heads(cfg, world_size: int, rank: int):
     return type(cfg)(**kwargs)
 
 
+def shard_requests_config(cfg, world_size: int, rank: int):
+    """Request shard of a config for one of ``world_size`` GPUs: ``batch / world_size`` of the
+    batch's (independently drawn) requests with all heads, in the rank's own pool and tables (the
+    partition used when the KV heads are fewer than the GPUs)."""
+    if cfg.batch % world_size != 0:
+        raise ValueError(f"a batch of {cfg.batch} does not split over {world_size} GPUs")
+    kwargs = dict(cfg.__dict__)
+    kwargs["batch"] = cfg.batch // world_size
+    kwargs["num_pages"] = max(1, cfg.num_pages // world_size)
+    kwargs["seed"] = cfg.seed * 131 + rank
+    return type(cfg)(**kwargs)
+
+
+def shard_config(cfg, world_size: int, rank: int):
+    """The partition a benchmark configuration names: by request for the 30B-A3B shape (4 KV
+    heads, up to 8 GPUs), by KV head otherwise.  Returns ``(config, kind)``."""
+    if world_size == 1:
+        return cfg, "single GPU"
+    if cfg.name.startswith("c3") or cfg.kv_heads % world_size != 0:
+        return shard_requests_config(cfg, world_size, rank), f"request shards over {world_size} GPUs, no collective"
+    return shard_kv_heads(cfg, world_size, rank), f"kv-head shards over {world_size} GPUs, no collective"
+
+
 def draw_lengths(cfg: DecodeConfig) -> np.ndarray:
     if cfg.len_dist == "fixed":
         return np.full(cfg.batch, cfg.len_lo, dtype=np.int64)

@@ -102,3 +102,14 @@ def test_shard_config_and_slices():
     full = G.build_decode("decode_gqa4_edges")
     parts = [W.shard_decode_requests(full, 4, r) for r in range(4)]
     assert sorted(int(x) for p in parts for x in p.seq_lens) == sorted(int(x) for x in full.seq_lens)
+
+
+def test_benchmark_partition_choice():
+    """KV-head shards where the heads divide, request shards for the 4-KV-head shape on 8 GPUs."""
+    cfg, kind = W.shard_config(W.C2, 8, 3)
+    assert (cfg.kv_heads, cfg.q_heads, cfg.batch) == (1, 8, 32) and kind.startswith("kv-head")
+    parts = [W.shard_config(W.C3, 8, r) for r in range(8)]
+    assert all(k.startswith("request") for _, k in parts)
+    assert sum(c.batch for c, _ in parts) == W.C3.batch and {c.kv_heads for c, _ in parts} == {W.C3.kv_heads}
+    assert len({c.seed for c, _ in parts}) == 8 and sum(c.num_pages for c, _ in parts) == W.C3.num_pages
+    assert W.shard_config(W.C2, 1, 0) == (W.C2, "single GPU")
