@@ -62,7 +62,7 @@ constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
 #define B200KV_DECODE_L2_PREFETCH 2   // tiles prefetched into L2 before the dependency wait (<= kLead)
 #endif
 #ifndef B200KV_DECODE_MIN_PAGES
-#define B200KV_DECODE_MIN_PAGES 8
+#define B200KV_DECODE_MIN_PAGES 4
 #endif
 constexpr int kMinPagesPerTeam = B200KV_DECODE_MIN_PAGES;   // a team is not worth launching for fewer pages
 constexpr int kCombineThreads = 256;   // at most; the launch picks 128 or 256
