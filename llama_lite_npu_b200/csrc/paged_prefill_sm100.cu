@@ -9,7 +9,10 @@
 // One CTA = one (request, 128-row query tile, PAIR of query heads of one GQA group): the two
 // heads are two 128 x 128 query tiles with identical causal structure that share every K/V tile,
 // so K/V cross L2 -> shared memory once for both and the tensor core always has the other tile's
-// MMAs to run while one tile is in its softmax.  Ten warps, one CTA per SM:
+// MMAs to run while one tile is in its softmax.  A CTA then does a SECOND query tile of the same
+// request and heads: tile t-1-k (many key tiles) is followed by tile k (few), which balances the
+// causal work across CTAs and lets the second tile's Q / K / V loads, barriers and TMEM be ready
+// while the first one drains.  Ten warps, one CTA per SM:
 //   warp 8  producer : TMA (cp.async.bulk.tensor) of both Q tiles once, then of the K and V pages
 //                      of each 128-key tile into a 3-slot ring of 32 KB slots in which K runs one
 //                      tile ahead of V (K_0 K_1 V_0 K_2 V_1 ...), the order in which the tensor
@@ -202,25 +205,44 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const int pair = static_cast<int>(blockIdx.x) - kv_head * pairs_per_group;
   const int head0 = kv_head * p.group + 2 * pair;          // query head of tile 0; tile 1 is head0 + 1
   const bool active1 = (2 * pair + 1) < p.group;            // an odd group leaves its last head alone
-  const int mt = p.tiles_m - 1 - static_cast<int>(blockIdx.y);
+  // A CTA takes up to TWO query tiles of its request, one after the other: tile t_b-1-k (many key
+  // tiles) and tile k (few), so every CTA of a request does about the same work, and the second
+  // tile's Q / K / V loads, barrier set-up and TMEM are already there when the first one drains.
+  const int pair_k = static_cast<int>(blockIdx.y);
   const int b = blockIdx.z;
-  int64_t q_len = load_len(p.q_lens, p.lens_i64, b);
-  int64_t ctx = load_len(p.ctx_lens, p.lens_i64, b);
+  const int64_t q_len = load_len(p.q_lens, p.lens_i64, b);
+  const int64_t ctx = load_len(p.ctx_lens, p.lens_i64, b);
   if (q_len < 0 || ctx < 0) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
     return;
   }
-  const int64_t row0 = static_cast<int64_t>(mt) * kBM;  // first query row of the tile in its request
-  if (row0 >= q_len) return;
-  const int rows = static_cast<int>(q_len - row0 < kBM ? q_len - row0 : kBM);
-  const int64_t q_tok0 = static_cast<int64_t>(__ldg(p.q_start + b)) + row0;  // packed row of tile row 0
-  if (q_tok0 < 0 || q_tok0 + rows > p.total_q) {
+  const int t_b = static_cast<int>((q_len + kBM - 1) / kBM);   // query tiles of the request
+  if (pair_k > t_b - 1 - pair_k) return;                        // also q_len == 0
+  const int n_work = pair_k < t_b - 1 - pair_k ? 2 : 1;
+  const int64_t q_start_b = static_cast<int64_t>(__ldg(p.q_start + b));
+  struct Work {
+    int64_t row0;      // first query row of the tile in its request
+    int rows;          // rows of the tile that exist
+    int64_t q_tok0;    // packed row of tile row 0
+    int64_t kv_len;    // keys visible to the tile's last row
+    int64_t n_pages;
+    int n_tiles;       // 128-key tiles
+  };
+  auto work_of = [&](int w) {
+    Work k;
+    k.row0 = static_cast<int64_t>(w == 0 ? t_b - 1 - pair_k : pair_k) * kBM;
+    k.rows = static_cast<int>(q_len - k.row0 < kBM ? q_len - k.row0 : kBM);
+    k.q_tok0 = q_start_b + k.row0;
+    k.kv_len = ctx + k.row0 + k.rows;
+    k.n_tiles = static_cast<int>((k.kv_len + kBN - 1) / kBN);
+    k.n_pages = (k.kv_len + kPS - 1) / kPS;
+    return k;
+  };
+  const Work work0 = work_of(0), work1 = work_of(n_work - 1);
+  if (work0.q_tok0 < 0 || work0.q_tok0 + work0.rows > p.total_q || work1.q_tok0 < 0) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
     return;
   }
-  const int64_t kv_len = ctx + row0 + rows;               // keys visible to the tile's last row
-  const int n_tiles = static_cast<int>((kv_len + kBN - 1) / kBN);
-  const int64_t n_pages = (kv_len + kPS - 1) / kPS;
   const int table_row = p.req_ids ? __ldg(p.req_ids + b) : b;
 
   // ---- shared memory carve-up -----------------------------------------------------------------
@@ -235,8 +257,9 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const uint32_t bar_pfull = bar_sfull + 8 * kGroups;       // [kGroups] P_g of a tile is in shared memory
   const uint32_t bar_pvfull = bar_pfull + 8 * kGroups;      // [kGroups] O_g += P_g V of a tile completed
   const uint32_t bar_sfree = bar_pvfull + 8 * kGroups;      // [kGroups] S_g of a tile is in registers
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_sfree + 8 * kGroups - sm_q));
-  static_assert(8 + 2 * 8 * kSlots + 4 * 8 * kGroups + 8 <= kBarBytes, "barrier area too small");
+  const uint32_t bar_qfree = bar_sfree + 8 * kGroups;       // every S of a query tile has completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + (bar_qfree + 8 - sm_q));
+  static_assert(8 + 2 * 8 * kSlots + 4 * 8 * kGroups + 8 + 8 <= kBarBytes, "barrier area too small");
   if ((sm_q & 1023u) != 0) {  // swizzled boxes and UMMA descriptors assume 1024-byte alignment
     set_status(p.status, B200KV_DEV_BAD_PAGE);
     return;
@@ -244,6 +267,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
+    mbar_init(bar_qfree, 1);
     for (int i = 0; i < kSlots; ++i) {
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, 1);
@@ -270,8 +294,10 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   // Ring order: K runs one tile ahead of V, K_0 K_1 V_0 K_2 V_1 ... K_{T-1} V_{T-2} V_{T-1}, which is
   // also the order in which the tensor core finishes with the tiles (S of tile j+1 is issued
   // before P V of tile j).  Item n lives in slot n % kSlots.
-  auto pos_k = [](int t) { return t == 0 ? 0 : 2 * t - 1; };
-  auto pos_v = [n_tiles](int t) { return t == n_tiles - 1 ? 2 * n_tiles - 1 : 2 * t + 2; };
+  // A query tile with T key tiles uses 2T consecutive ring items starting at `base`; barrier
+  // phases simply keep counting across the CTA's query tiles.
+  auto pos_k = [](int base, int t) { return base + (t == 0 ? 0 : 2 * t - 1); };
+  auto pos_v = [](int base, int T, int t) { return base + (t == T - 1 ? 2 * T - 1 : 2 * t + 2); };
   cudaGridDependencySynchronize();  // q and the pool belong to earlier kernels until here
   cudaTriggerProgrammaticLaunchCompletion();
 
@@ -284,73 +310,87 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       prefetch_tensormap(&qmap);
       prefetch_tensormap(&kmap);
       prefetch_tensormap(&vmap);
-      mbar_arrive_expect_tx(bar_q, (active1 ? 2 : 1) * kQBytes);
-      // Rows past this request's q_len are the next request's rows (or zero fill past the end);
-      // their results are never stored.
-      const int qt = static_cast<int>(q_tok0);
-      tma_load_3d(sm_q, &qmap, bar_q, 0, head0, qt, policy);
-      tma_load_3d(sm_q + kQBytes / 2, &qmap, bar_q, 64, head0, qt, policy);
-      if (active1) {
-        tma_load_3d(sm_q + kQBytes, &qmap, bar_q, 0, head0 + 1, qt, policy);
-        tma_load_3d(sm_q + kQBytes + kQBytes / 2, &qmap, bar_q, 64, head0 + 1, qt, policy);
-      }
     }
     const int my_page = lane >> 1;   // lanes 0..15: page of the tile
     const int my_half = lane & 1;    // low / high half of head_dim
     const int32_t* trow = p.table + static_cast<int64_t>(table_row) * p.table_row_stride;
-    const int64_t dense0 = static_cast<int64_t>(__ldg(p.q_start + b));
-    // Raw table entry of this lane's page of a tile (0 when the page does not exist).
-    auto fetch_id = [&](int j) -> int32_t {
-      const int64_t lp = static_cast<int64_t>(j) * kTilePages + my_page;
-      if (lane >= 16 || j >= n_tiles || lp >= n_pages || p.table_kind == B200KV_TABLE_DENSE) return 0;
-      return __ldg(trow + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
-    };
-    // Item n of the ring order above: which tile, and K or V.
-    auto item_tile = [n_tiles](int n, bool& is_v) {
-      if (n == 0) { is_v = false; return 0; }
-      if (n == 2 * n_tiles - 1) { is_v = true; return n_tiles - 1; }
-      is_v = (n & 1) == 0;
-      return is_v ? (n - 2) / 2 : (n + 1) / 2;
-    };
-    bool v_cur;
-    int t_cur = item_tile(0, v_cur);
-    int32_t id_cur = fetch_id(t_cur);
     bool ok = true;
-    for (int n = 0; ok && n < 2 * n_tiles; ++n) {
-      bool v_next = false;
-      const int t_next = n + 1 < 2 * n_tiles ? item_tile(n + 1, v_next) : n_tiles;
-      const int32_t id_next = fetch_id(t_next);   // in flight while this item is issued
-      const int64_t page0 = static_cast<int64_t>(t_cur) * kTilePages;
-      const int np = static_cast<int>(n_pages - page0 < kTilePages ? n_pages - page0 : kTilePages);
-      const int64_t lp = page0 + my_page;
-      int64_t slot;
-      if (p.table_kind == B200KV_TABLE_BLOCK) slot = static_cast<int64_t>(id_cur) * kPS;
-      else if (p.table_kind == B200KV_TABLE_TOKEN) slot = static_cast<int64_t>(id_cur);
-      else slot = dense0 + lp * kPS;   // dense packed K/V: token t of the request at q_start + t
-      if (lane < 2 * np && (slot < 0 || slot >= p.pool_tokens)) {
-        set_status(p.status, B200KV_DEV_BAD_PAGE);
-        slot = 0;  // never dereference a bad entry: report it and read page 0 instead
-      }
-      const uint32_t dst_off = my_half * (kTileBytes / 2) + my_page * kHalfPage;
-      const int sl = n % kSlots;
-      if (n >= kSlots && !mbar_wait_bounded(bar_empty + 8 * sl, ((n / kSlots) - 1) & 1)) {
+    int item_base = 0;
+    for (int w = 0; ok && w < n_work; ++w) {
+      const Work wk = w ? work1 : work0;
+      const int n_tiles = wk.n_tiles;
+      const int64_t n_pages = wk.n_pages;
+      // ---- both Q tiles of this query tile (the previous one's S MMAs must be done with them)
+      if (w > 0 && !mbar_wait_bounded(bar_qfree, (w - 1) & 1)) {
         set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-        ok = false;
         break;
       }
-      if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * sl, np * 2 * kHalfPage);
-      __syncwarp();
-      if (lane < 2 * np)
-        tma_load_3d(sm_ring + sl * kTileBytes + dst_off, v_cur ? &vmap : &kmap, bar_full + 8 * sl, my_half * 64,
-                    kv_head, static_cast<int>(slot), policy);
-      t_cur = t_next;
-      v_cur = v_next;
-      id_cur = id_next;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar_q, (active1 ? 2 : 1) * kQBytes);
+        // Rows past this request's q_len are the next request's rows (or zero fill past the end);
+        // their results are never stored.
+        const int qt = static_cast<int>(wk.q_tok0);
+        tma_load_3d(sm_q, &qmap, bar_q, 0, head0, qt, policy);
+        tma_load_3d(sm_q + kQBytes / 2, &qmap, bar_q, 64, head0, qt, policy);
+        if (active1) {
+          tma_load_3d(sm_q + kQBytes, &qmap, bar_q, 0, head0 + 1, qt, policy);
+          tma_load_3d(sm_q + kQBytes + kQBytes / 2, &qmap, bar_q, 64, head0 + 1, qt, policy);
+        }
+      }
+      // Raw table entry of this lane's page of a tile (0 when the page does not exist).
+      auto fetch_id = [&](int j) -> int32_t {
+        const int64_t lp = static_cast<int64_t>(j) * kTilePages + my_page;
+        if (lane >= 16 || j >= n_tiles || lp >= n_pages || p.table_kind == B200KV_TABLE_DENSE) return 0;
+        return __ldg(trow + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
+      };
+      // Item n of the ring order above: which tile, and K or V.
+      auto item_tile = [n_tiles](int n, bool& is_v) {
+        if (n == 0) { is_v = false; return 0; }
+        if (n == 2 * n_tiles - 1) { is_v = true; return n_tiles - 1; }
+        is_v = (n & 1) == 0;
+        return is_v ? (n - 2) / 2 : (n + 1) / 2;
+      };
+      bool v_cur;
+      int t_cur = item_tile(0, v_cur);
+      int32_t id_cur = fetch_id(t_cur);
+      for (int nl = 0; ok && nl < 2 * n_tiles; ++nl) {
+        bool v_next = false;
+        const int t_next = nl + 1 < 2 * n_tiles ? item_tile(nl + 1, v_next) : n_tiles;
+        const int32_t id_next = fetch_id(t_next);   // in flight while this item is issued
+        const int64_t page0 = static_cast<int64_t>(t_cur) * kTilePages;
+        const int np = static_cast<int>(n_pages - page0 < kTilePages ? n_pages - page0 : kTilePages);
+        const int64_t lp = page0 + my_page;
+        int64_t slot;
+        if (p.table_kind == B200KV_TABLE_BLOCK) slot = static_cast<int64_t>(id_cur) * kPS;
+        else if (p.table_kind == B200KV_TABLE_TOKEN) slot = static_cast<int64_t>(id_cur);
+        else slot = q_start_b + lp * kPS;   // dense packed K/V: token t of the request at q_start + t
+        if (lane < 2 * np && (slot < 0 || slot >= p.pool_tokens)) {
+          set_status(p.status, B200KV_DEV_BAD_PAGE);
+          slot = 0;  // never dereference a bad entry: report it and read page 0 instead
+        }
+        const uint32_t dst_off = my_half * (kTileBytes / 2) + my_page * kHalfPage;
+        const int n = item_base + nl;
+        const int sl = n % kSlots;
+        if (n >= kSlots && !mbar_wait_bounded(bar_empty + 8 * sl, ((n / kSlots) - 1) & 1)) {
+          set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+        if (lane == 0) mbar_arrive_expect_tx(bar_full + 8 * sl, np * 2 * kHalfPage);
+        __syncwarp();
+        if (lane < 2 * np)
+          tma_load_3d(sm_ring + sl * kTileBytes + dst_off, v_cur ? &vmap : &kmap, bar_full + 8 * sl, my_half * 64,
+                      kv_head, static_cast<int>(slot), policy);
+        t_cur = t_next;
+        v_cur = v_next;
+        id_cur = id_next;
+      }
+      item_base += 2 * n_tiles;
     }
   } else if (warp == kMmaWarp) {
     // ============================== MMA issuer ==============================================
     if (lane == 0) {
-      bool ok = mbar_wait_bounded(bar_q, 0);
+      bool ok = true;
       // Descriptors are built once; per instruction only the 14-bit start-address field (bytes
       // >> 4, shared-memory addresses fit without carry) is advanced by a compile-time constant.
       // K is the K-major B operand of S; V is the MN-major B operand of P V: 64 head_dim values
@@ -363,8 +403,9 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       constexpr uint64_t kSlotStep = kTileBytes >> 4;
       constexpr uint64_t kChunkStep = (kTileBytes / 2) >> 4;   // second 64-wide chunk of an operand tile
 
+      int tile_base = 0, item_base = 0, n_tiles = 0;   // of the query tile being issued
       auto issue_s = [&](int g, int j) {            // S_g = Q_g K_j^T : 8 x (M128 N128 K16)
-        const uint64_t kd = dk_base + static_cast<uint64_t>(pos_k(j) % kSlots) * kSlotStep;
+        const uint64_t kd = dk_base + static_cast<uint64_t>(pos_k(item_base, j) % kSlots) * kSlotStep;
         const uint64_t qd = g ? dq1 : dq0;
         const uint32_t d_s = tmem_base + kTmemS + g * kBN;
         tc_fence_after();
@@ -377,7 +418,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         umma_commit(bar_sfull + 8 * g);
       };
       auto issue_pv = [&](int g, int j) {           // O_g += P_g V_j : 8 x (M128 N128 K16)
-        const uint64_t vd = dv_base + static_cast<uint64_t>(pos_v(j) % kSlots) * kSlotStep;
+        const uint64_t vd = dv_base + static_cast<uint64_t>(pos_v(item_base, n_tiles, j) % kSlots) * kSlotStep;
         const uint64_t pd = g ? dp1 : dp0;
         const uint32_t d_o = tmem_base + kTmemO + g * kD;
         tc_fence_after();
@@ -391,47 +432,62 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         umma_commit(bar_pvfull + 8 * g);
       };
       const int ng = active1 ? 2 : 1;
-      // Tensor-core order: S0_0 S1_0 | S0_1 S1_1 PV0_0 PV1_0 | S0_2 S1_2 PV0_1 PV1_1 | ...  The S of
-      // tile j+1 is issued as soon as the softmax group holds S of tile j in registers, so it runs
-      // under that softmax and the group does not wait for its next S.
-      if (ok) ok = mbar_wait_bounded(bar_full + 8 * 0, 0);
-      if (ok) {
-        for (int g = 0; g < ng; ++g) issue_s(g, 0);
-        umma_commit(bar_empty + 8 * 0);                     // K_0: both S issued
-      }
+      // Tensor-core order within a query tile: S0_0 S1_0 | S0_1 S1_1 PV0_0 PV1_0 | S0_2 S1_2 PV0_1
+      // PV1_1 | ...  The S of key tile j+1 is issued as soon as the softmax group holds S of tile j in
+      // registers, so it runs under that softmax and the group does not wait for its next S.
+      //
       // This thread paces the CTA (the tensor core idles whenever it is not issuing), and a barrier
       // test costs it a few hundred cycles even when the phase is long complete.  So the three
       // barriers a step depends on are tested together (independent instructions, one latency)
       // and only the ones that were not ready are waited for.
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j + 1 < n_tiles) {
-          const int pk = pos_k(j + 1);
-          const uint32_t b_k = bar_full + 8 * (pk % kSlots), par_k = (pk / kSlots) & 1;
-          const bool r_k = mbar_test_wait(b_k, par_k);
-          const bool r_0 = mbar_test_wait(bar_sfree, j & 1);
-          const bool r_1 = ng > 1 ? mbar_test_wait(bar_sfree + 8, j & 1) : true;
-          if (!r_k && !mbar_wait_bounded(b_k, par_k)) { ok = false; break; }
-          if (!r_0 && !mbar_wait_bounded(bar_sfree, j & 1)) { ok = false; break; }
-          issue_s(0, j + 1);
-          if (ng > 1) {
-            if (!r_1 && !mbar_wait_bounded(bar_sfree + 8, j & 1)) { ok = false; break; }
-            issue_s(1, j + 1);
+      for (int w = 0; ok && w < n_work; ++w) {
+        n_tiles = (w ? work1 : work0).n_tiles;
+        // ---- first S of the query tile: its Q, its K_0, and (second tile) the S registers of the
+        // previous tile's last key tile
+        ok = mbar_wait_bounded(bar_q, w & 1);
+        const int pk0 = pos_k(item_base, 0);
+        if (ok) ok = mbar_wait_bounded(bar_full + 8 * (pk0 % kSlots), (pk0 / kSlots) & 1);
+        for (int g = 0; ok && g < ng; ++g) {
+          if (w > 0) ok = mbar_wait_bounded(bar_sfree + 8 * g, (tile_base - 1) & 1);
+          if (ok) issue_s(g, 0);
+        }
+        if (!ok) break;
+        umma_commit(bar_empty + 8 * (pk0 % kSlots));        // K_0: both S issued
+        if (n_tiles == 1) umma_commit(bar_qfree);           // the Q tiles may be replaced
+        for (int j = 0; ok && j < n_tiles; ++j) {
+          const uint32_t par = (tile_base + j) & 1;         // phase of the per-key-tile barriers
+          if (j + 1 < n_tiles) {
+            const int pk = pos_k(item_base, j + 1);
+            const uint32_t b_k = bar_full + 8 * (pk % kSlots), par_k = (pk / kSlots) & 1;
+            const bool r_k = mbar_test_wait(b_k, par_k);
+            const bool r_0 = mbar_test_wait(bar_sfree, par);
+            const bool r_1 = ng > 1 ? mbar_test_wait(bar_sfree + 8, par) : true;
+            if (!r_k && !mbar_wait_bounded(b_k, par_k)) { ok = false; break; }
+            if (!r_0 && !mbar_wait_bounded(bar_sfree, par)) { ok = false; break; }
+            issue_s(0, j + 1);
+            if (ng > 1) {
+              if (!r_1 && !mbar_wait_bounded(bar_sfree + 8, par)) { ok = false; break; }
+              issue_s(1, j + 1);
+            }
+            umma_commit(bar_empty + 8 * (pk % kSlots));     // K_{j+1}: both S issued
+            if (j + 2 == n_tiles) umma_commit(bar_qfree);   // that was the query tile's last S
           }
-          umma_commit(bar_empty + 8 * (pk % kSlots));       // K_{j+1}: both S issued
+          const int pv = pos_v(item_base, n_tiles, j);
+          const uint32_t b_v = bar_full + 8 * (pv % kSlots), par_v = (pv / kSlots) & 1;
+          const bool r_v = mbar_test_wait(b_v, par_v);
+          const bool r_0 = mbar_test_wait(bar_pfull, par);
+          const bool r_1 = ng > 1 ? mbar_test_wait(bar_pfull + 8, par) : true;
+          if (!r_v && !mbar_wait_bounded(b_v, par_v)) { ok = false; break; }
+          if (!r_0 && !mbar_wait_bounded(bar_pfull, par)) { ok = false; break; }
+          issue_pv(0, j);
+          if (ng > 1) {
+            if (!r_1 && !mbar_wait_bounded(bar_pfull + 8, par)) { ok = false; break; }
+            issue_pv(1, j);
+          }
+          umma_commit(bar_empty + 8 * (pv % kSlots));       // V_j: both P V issued
         }
-        const int pv = pos_v(j);
-        const uint32_t b_v = bar_full + 8 * (pv % kSlots), par_v = (pv / kSlots) & 1;
-        const bool r_v = mbar_test_wait(b_v, par_v);
-        const bool r_0 = mbar_test_wait(bar_pfull, j & 1);
-        const bool r_1 = ng > 1 ? mbar_test_wait(bar_pfull + 8, j & 1) : true;
-        if (!r_v && !mbar_wait_bounded(b_v, par_v)) { ok = false; break; }
-        if (!r_0 && !mbar_wait_bounded(bar_pfull, j & 1)) { ok = false; break; }
-        issue_pv(0, j);
-        if (ng > 1) {
-          if (!r_1 && !mbar_wait_bounded(bar_pfull + 8, j & 1)) { ok = false; break; }
-          issue_pv(1, j);
-        }
-        umma_commit(bar_empty + 8 * (pv % kSlots));         // V_j: both P V issued
+        tile_base += n_tiles;
+        item_base += 2 * n_tiles;
       }
       if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
     }
@@ -450,11 +506,17 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
     const uint32_t tmem_o = tmem_base + t_lane + kTmemO + g * kD;
     const uint32_t my_p = sm_p + g * kPBytes;
     const uint32_t b_sfull = bar_sfull + 8 * g, b_pfull = bar_pfull + 8 * g, b_pvfull = bar_pvfull + 8 * g;
+    bool ok = true;
+    int tile_base = 0, item_base = 0;
+    for (int w = 0; active && ok && w < n_work; ++w) {
+    const Work wk = w ? work1 : work0;
+    const int n_tiles = wk.n_tiles;
+    const int64_t row0 = wk.row0, kv_len = wk.kv_len;
     const int64_t q_pos = ctx + row0 + row;                // logical position of this query row
     float m_used = -INFINITY, l_run = 0.f;
-    bool ok = true;
-    for (int j = 0; active && j < n_tiles; ++j) {
-      if (!mbar_wait_bounded(b_sfull, j & 1)) { ok = false; break; }
+    for (int j = 0; j < n_tiles; ++j) {
+      const uint32_t par = (tile_base + j) & 1;            // phase of the per-key-tile barriers
+      if (!mbar_wait_bounded(b_sfull, par)) { ok = false; break; }
       tc_fence_after();
       const int64_t key0 = static_cast<int64_t>(j) * kBN;
       // Only tiles that reach past the first row's diagonal need the causal mask (warp-uniform).
@@ -484,7 +546,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       mx *= p.scale_log2;
       // P_g and O_g are free once the P V MMAs of tile j-1 have completed (they were issued
       // before this tile's S, so this wait is normally already satisfied).
-      if (j > 0 && !mbar_wait_bounded(b_pvfull, (j - 1) & 1)) { ok = false; break; }
+      if (j > 0 && !mbar_wait_bounded(b_pvfull, par ^ 1)) { ok = false; break; }
       const bool grow = mx > m_used + 8.f;                 // also true on the first tile (m_used = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_used;
@@ -547,7 +609,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         // slots; their P is 0 but 0 * NaN would still poison the row, so zero those V rows.  Each
         // group does the whole clean-up before publishing its own P, which is what its own P V
         // waits for; the two groups write the same zeros.
-        const int item = pos_v(j);
+        const int item = pos_v(item_base, n_tiles, j);
         const int sl = item % kSlots;
         const int valid = static_cast<int>(kv_len - key0);
         if (valid < kBN) {
@@ -565,12 +627,13 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       fence_proxy_async_smem();                            // P (and V fix-ups) visible to the tensor core
       mbar_arrive(b_pfull);
     }
-    if (active && ok && !mbar_wait_bounded(b_pvfull, (n_tiles - 1) & 1)) ok = false;
-    if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-    if (active && ok) {
+    // ---- the query tile's rows: O / l, once its last P V has completed -----------------------
+    if (ok && !mbar_wait_bounded(b_pvfull, (tile_base + n_tiles - 1) & 1)) ok = false;
+    if (ok) {
       tc_fence_after();
       const float inv = 1.f / l_run;
-      __half* op = p.out + (q_tok0 + row) * p.out_stride_t + static_cast<int64_t>(head0 + g) * p.out_stride_h;
+      const int rows = wk.rows;
+      __half* op = p.out + (wk.q_tok0 + row) * p.out_stride_t + static_cast<int64_t>(head0 + g) * p.out_stride_h;
 #pragma unroll 1
       for (int q4 = 0; q4 < kD / 32; ++q4) {
         uint32_t ov[32];
@@ -590,6 +653,10 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       }
       tc_fence_before();
     }
+    tile_base += n_tiles;
+    item_base += 2 * n_tiles;
+    }  // query tiles of this CTA
+    if (!ok) set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
   }
 
   // ---- common exit: every warp gets here (all waits above are bounded) ----------------------
@@ -659,7 +726,7 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   p.out_stride_h = a.out_stride_h;
   p.status = a.status;
   p.tiles_m = static_cast<int>((a.max_q_len + kBM - 1) / kBM);
-  if (p.tiles_m > 65535) return B200KV_ETOOLARGE;
+  if (p.tiles_m > 2 * 65535) return B200KV_ETOOLARGE;
 
   static bool attr_done[64] = {};
   int dev = 0;
@@ -676,7 +743,7 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   cudaLaunchConfig_t cfg{};
   // x: (KV head, pair of query heads of its group), adjacent so a group's CTAs share K/V in L2.
   cfg.gridDim = dim3(static_cast<unsigned>(a.kv_heads * ((p.group + 1) / 2)),
-                     static_cast<unsigned>(p.tiles_m), static_cast<unsigned>(a.batch));
+                     static_cast<unsigned>((p.tiles_m + 1) / 2), static_cast<unsigned>(a.batch));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
