@@ -449,3 +449,15 @@ def test_bounded_wait_times_out_cleanly_and_context_survives(built_lib):
     got = _decode_gpu(c, "block")
     want = O.paged_decode(c.q, c.k_cache, c.v_cache, SCALE, c.token_table, c.seq_lens_t)
     assert _maxdiff(got, want) <= ATTN_TOL
+
+
+@pytest.mark.parametrize("group,kvh", [(1, 2), (3, 1), (8, 1)])
+def test_prefill_tile_pairs_odd_even_counts(group, kvh):
+    """A CTA does two query tiles of its request (t-1-k then k): requests with 2, 5, 8 and 11 query
+    tiles (an odd count leaves the middle tile alone), with and without history, odd head groups."""
+    prompts = np.array([129 + 16 * 0, 640, 1000, 1281 + 16 * 40])
+    shared = np.array([0, 16, 3, 40])
+    cfg = W.PrefillConfig(f"pairs{group}", 4, group * kvh, kvh, 1024, 1, 1, seed=77 + group)
+    c = W.make_prefill_case(cfg, fill="hash", prompt_lens=prompts, shared_pages=shared)
+    got, _ = _prefill_gpu(c, "block")
+    assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
