@@ -633,24 +633,44 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       tc_fence_after();
       const float inv = 1.f / l_run;
       const int rows = wk.rows;
-      __half* op = p.out + (wk.q_tok0 + row) * p.out_stride_t + static_cast<int64_t>(head0 + g) * p.out_stride_h;
+      // O / l -> fp16, staged through the group's (now idle) P buffer so that the global stores are
+      // whole 256-byte rows: written straight from the registers, a warp's 16-byte stores would
+      // land in 32 different rows (16 KB apart) and the read-out took ~6 000 cycles per query tile.
+      // Staging layout: row r at r * 256 B, its sixteen 16-byte chunks XOR-ed with r % 16 (no
+      // bank conflicts either way).
 #pragma unroll 1
       for (int q4 = 0; q4 < kD / 32; ++q4) {
         uint32_t ov[32];
         tmem_ld32(tmem_o + q4 * 32, ov);                   // warp-collective: every lane takes part
         tmem_ld_wait();
-        if (row < rows) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_half2(__uint_as_float(ov[c * 8 + 0]) * inv, __uint_as_float(ov[c * 8 + 1]) * inv);
-            v.y = pack_half2(__uint_as_float(ov[c * 8 + 2]) * inv, __uint_as_float(ov[c * 8 + 3]) * inv);
-            v.z = pack_half2(__uint_as_float(ov[c * 8 + 4]) * inv, __uint_as_float(ov[c * 8 + 5]) * inv);
-            v.w = pack_half2(__uint_as_float(ov[c * 8 + 6]) * inv, __uint_as_float(ov[c * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + q4 * 32 + c * 8) = v;
-          }
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t v0 = pack_half2(__uint_as_float(ov[c * 8 + 0]) * inv, __uint_as_float(ov[c * 8 + 1]) * inv);
+          const uint32_t v1 = pack_half2(__uint_as_float(ov[c * 8 + 2]) * inv, __uint_as_float(ov[c * 8 + 3]) * inv);
+          const uint32_t v2 = pack_half2(__uint_as_float(ov[c * 8 + 4]) * inv, __uint_as_float(ov[c * 8 + 5]) * inv);
+          const uint32_t v3 = pack_half2(__uint_as_float(ov[c * 8 + 6]) * inv, __uint_as_float(ov[c * 8 + 7]) * inv);
+          asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(
+                           my_p + row * 256 + (((q4 * 4 + c) ^ (row & 15)) << 4)),
+                       "r"(v0), "r"(v1), "r"(v2), "r"(v3)
+                       : "memory");
         }
       }
+      asm volatile("bar.sync %0, %1;\n" ::"r"(2 + g), "n"(kGroupWarps * 32) : "memory");
+      __half* obase = p.out + wk.q_tok0 * p.out_stride_t + static_cast<int64_t>(head0 + g) * p.out_stride_h;
+#pragma unroll 4
+      for (int it = 0; it < kBM * 16 / (kGroupWarps * 32); ++it) {
+        const int idx = it * (kGroupWarps * 32) + gtid;    // half a warp per row
+        const int r = idx >> 4, c = idx & 15;
+        if (r < rows) {
+          uint4 v;
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
+                       : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "r"(my_p + r * 256 + ((c ^ (r & 15)) << 4)));
+          *reinterpret_cast<uint4*>(obase + static_cast<int64_t>(r) * p.out_stride_t + c * 8) = v;
+        }
+      }
+      // the P buffer goes back to the next query tile's softmax only when everybody has read it
+      asm volatile("bar.sync %0, %1;\n" ::"r"(2 + g), "n"(kGroupWarps * 32) : "memory");
       tc_fence_before();
     }
     tile_base += n_tiles;
