@@ -638,17 +638,18 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       // land in 32 different rows (16 KB apart) and the read-out took ~6 000 cycles per query tile.
       // Staging layout: row r at r * 256 B, its sixteen 16-byte chunks XOR-ed with r % 16 (no
       // bank conflicts either way).
-#pragma unroll 1
+      uint32_t ov[4][32];                                  // the S registers are dead here
+#pragma unroll
+      for (int q4 = 0; q4 < kD / 32; ++q4) tmem_ld32(tmem_o + q4 * 32, ov[q4]);   // warp-collective, all in flight
+      tmem_ld_wait();
+#pragma unroll
       for (int q4 = 0; q4 < kD / 32; ++q4) {
-        uint32_t ov[32];
-        tmem_ld32(tmem_o + q4 * 32, ov);                   // warp-collective: every lane takes part
-        tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          const uint32_t v0 = pack_half2(__uint_as_float(ov[c * 8 + 0]) * inv, __uint_as_float(ov[c * 8 + 1]) * inv);
-          const uint32_t v1 = pack_half2(__uint_as_float(ov[c * 8 + 2]) * inv, __uint_as_float(ov[c * 8 + 3]) * inv);
-          const uint32_t v2 = pack_half2(__uint_as_float(ov[c * 8 + 4]) * inv, __uint_as_float(ov[c * 8 + 5]) * inv);
-          const uint32_t v3 = pack_half2(__uint_as_float(ov[c * 8 + 6]) * inv, __uint_as_float(ov[c * 8 + 7]) * inv);
+          const uint32_t v0 = pack_half2(__uint_as_float(ov[q4][c * 8 + 0]) * inv, __uint_as_float(ov[q4][c * 8 + 1]) * inv);
+          const uint32_t v1 = pack_half2(__uint_as_float(ov[q4][c * 8 + 2]) * inv, __uint_as_float(ov[q4][c * 8 + 3]) * inv);
+          const uint32_t v2 = pack_half2(__uint_as_float(ov[q4][c * 8 + 4]) * inv, __uint_as_float(ov[q4][c * 8 + 5]) * inv);
+          const uint32_t v3 = pack_half2(__uint_as_float(ov[q4][c * 8 + 6]) * inv, __uint_as_float(ov[q4][c * 8 + 7]) * inv);
           asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};\n" ::"r"(
                            my_p + row * 256 + (((q4 * 4 + c) ^ (row & 15)) << 4)),
                        "r"(v0), "r"(v1), "r"(v2), "r"(v3)
