@@ -65,6 +65,15 @@ constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
 #define B200KV_DECODE_MIN_PAGES 4
 #endif
 constexpr int kMinPagesPerTeam = B200KV_DECODE_MIN_PAGES;   // a team is not worth launching for fewer pages
+// Ending a piece (merging the four warps' state, writing the rows, restarting on another
+// sequence) costs a CTA about as much as streaming this many pages.  The page line is therefore
+// split in UNITS: every non-empty sequence counts its pages plus this constant, so that teams
+// with more sequence boundaries get fewer pages; a team boundary that falls inside a sequence's
+// extra units snaps to the start of that sequence.
+#ifndef B200KV_DECODE_PIECE_COST
+#define B200KV_DECODE_PIECE_COST 8
+#endif
+constexpr int kPieceCost = B200KV_DECODE_PIECE_COST;
 constexpr int kCombineThreads = 256;   // at most; the launch picks 128 or 256
 
 struct DecodeParams {
@@ -273,25 +282,33 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     fence_barrier_init();
   }
 
-  // ---- where does this team's page range start? -------------------------------------------
-  // Thread t < 128 sums the pages of sequences [t*per, (t+1)*per); an exclusive scan over the
-  // 128 sums gives NP and the chunk holding the range start, then a short linear walk finds it.
+  // ---- where does this team's range start and end? -----------------------------------------
+  // Thread t < 128 sums the units (pages + kPieceCost per non-empty sequence) and the non-empty
+  // sequences of [t*per, (t+1)*per); scans over the 128 sums give the totals and the chunk holding
+  // a boundary, then a short linear walk finds the sequence.
+  int* scan_k = scan + kScanThreads + 1;   // non-empty sequences, same indexing
   const int per = (p.batch + kScanThreads - 1) / kScanThreads;
   if (tid < kScanThreads) {
-    int sum = 0;
+    int sum = 0, cnt = 0;
     const int lo = tid * per;
     const int hi = min(p.batch, lo + per);
-    for (int b = lo; b < hi; ++b) sum += pages_of(seq_len_checked(p, b));
+    for (int b = lo; b < hi; ++b) {
+      const int np = pages_of(seq_len_checked(p, b));
+      sum += np + (np > 0 ? kPieceCost : 0);
+      cnt += np > 0;
+    }
     scan[tid + 1] = sum;
-    if (tid == 0) scan[0] = 0;
+    scan_k[tid + 1] = cnt;
+    if (tid == 0) scan[0] = scan_k[0] = 0;
   }
   __syncthreads();
-  if (warp == 0) {  // inclusive scan of scan[1..128] by one warp, 4 values per lane
+  if (warp < 2) {  // inclusive scans of [1..128] by one warp each, 4 values per lane
+    int* arr = warp == 0 ? scan : scan_k;
     int v[4];
     int run = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      run += scan[1 + lane * 4 + i];
+      run += arr[1 + lane * 4 + i];
       v[i] = run;
     }
     int incl = run;
@@ -302,34 +319,56 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     }
     const int excl = incl - run;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) scan[1 + lane * 4 + i] = v[i] + excl;
+    for (int i = 0; i < 4; ++i) arr[1 + lane * 4 + i] = v[i] + excl;
   }
   __syncthreads();
-  const int64_t np_total = scan[kScanThreads];
+  const int64_t units_total = scan[kScanThreads];
+  const int64_t np_total = units_total - static_cast<int64_t>(kPieceCost) * scan_k[kScanThreads];
   const int nteams_eff = effective_teams(p.nteams, np_total);
   if (np_total == 0 || team >= nteams_eff) return;
-  const int64_t r_begin = team_begin(team, nteams_eff, np_total);
-  const int64_t r_end = team_begin(team + 1, nteams_eff, np_total);
 
-  int start_b, start_page;
-  {
-    // last chunk whose prefix <= r_begin
-    int lo = 0, hi = kScanThreads - 1;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (scan[mid] <= r_begin) lo = mid; else hi = mid - 1;
+  // Unit position x -> (sequence, page inside it, flat page index).  Positions inside a sequence's
+  // kPieceCost extra units map to its first page.
+  int start_b = 0, start_page = 0;
+  int64_t r_begin = 0, r_end = 0;
+#pragma unroll 1
+  for (int side = 0; side < 2; ++side) {
+    const int64_t x = team_begin(team + side, nteams_eff, units_total);
+    int64_t flat;
+    int sb = 0, sp = 0;
+    if (x >= units_total) {
+      flat = np_total;
+    } else {
+      int lo = 0, hi = kScanThreads - 1;   // last chunk whose unit prefix <= x
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (scan[mid] <= x) lo = mid; else hi = mid - 1;
+      }
+      int64_t acc = scan[lo];
+      int64_t pages_before = acc - static_cast<int64_t>(kPieceCost) * scan_k[lo];
+      int b = lo * per;
+      for (;;) {
+        const int np = pages_of(seq_len_checked(p, b));
+        const int w = np + (np > 0 ? kPieceCost : 0);
+        if (acc + w > x) break;
+        acc += w;
+        pages_before += np;
+        ++b;
+      }
+      const int64_t o = x - acc - kPieceCost;
+      sb = b;
+      sp = o > 0 ? static_cast<int>(o) : 0;
+      flat = pages_before + sp;
     }
-    int64_t acc = scan[lo];
-    int b = lo * per;
-    for (;;) {
-      const int np = pages_of(seq_len_checked(p, b));
-      if (acc + np > r_begin) break;
-      acc += np;
-      ++b;
+    if (side == 0) {
+      start_b = sb;
+      start_page = sp;
+      r_begin = flat;
+    } else {
+      r_end = flat;
     }
-    start_b = b;
-    start_page = static_cast<int>(r_begin - acc);
   }
+  if (r_end <= r_begin) return;   // a range that lay wholly inside a sequence's extra units
   __syncthreads();  // the scan scratch aliases the merge buffer; barrier inits are visible
 
   // ================================= producer warp ==========================================
@@ -618,12 +657,15 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
   const int lane = tid & 31;
   const int warp = tid >> 5;
 
+  // `before` in units (pages + kPieceCost per non-empty sequence, as in the split kernel);
+  // `total` carries the pages in its high half and the units in its low half
   long long before = 0, total = 0;
   const int nthreads = blockDim.x, nwarps = nthreads >> 5;
   for (int i = tid; i < p.batch; i += nthreads) {
     const int np = pages_of(seq_len_checked(p, i));
-    total += np;
-    if (i < b) before += np;
+    const int w = np + (np > 0 ? kPieceCost : 0);
+    total += (static_cast<long long>(np) << 32) + w;
+    if (i < b) before += w;
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
@@ -653,9 +695,10 @@ __global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeP
     return;
   }
   const int np = pages_of(len);
-  const int nteams_eff = effective_teams(p.nteams, total);
-  const int t_first = team_of(before, nteams_eff, total);
-  const int t_last = team_of(before + np - 1, nteams_eff, total);
+  const long long total_pages = total >> 32, total_units = total & 0xffffffffll;
+  const int nteams_eff = effective_teams(p.nteams, total_pages);
+  const int t_first = team_of(before + kPieceCost, nteams_eff, total_units);
+  const int t_last = team_of(before + kPieceCost + np - 1, nteams_eff, total_units);
   const int npieces = t_last - t_first + 1;
   if (npieces == 1) return;  // the split kernel wrote the final rows itself
 
