@@ -9,11 +9,13 @@
 // byte leaves HBM once.  Scheduling is a static "flat page line" decomposition:
 //
 //   * all sequences' pages are laid end to end (NP = sum_b ceil(L_b / 16) pages);
-//   * the launch has `nteams` teams of Hkv CTAs; team i takes the contiguous page range
-//     [i*NP/nteams, (i+1)*NP/nteams) and CTA k of the team handles KV head k over it, so
-//     every CTA streams the same number of bytes (+-1 page) whatever the length mix, and
-//     the Hkv CTAs of a team sweep the same token rows (one 2*Hkv*128-half pool row holds
-//     all heads of a token) at the same time;
+//   * the launch has `nteams` teams of Hkv CTAs; team i takes the contiguous range
+//     [i*U/nteams, (i+1)*U/nteams) of that line and CTA k of the team handles KV head k over
+//     it, so every CTA has the same work whatever the length mix, and the Hkv CTAs of a team
+//     sweep the same token rows (one 2*Hkv*128-half pool row holds all heads of a token) at
+//     the same time.  The line is measured in units, U = NP + kPieceCost per non-empty
+//     sequence: ending a piece costs a CTA about that many pages of streaming, and a cut
+//     inside a sequence's extra units snaps to the start of the sequence;
 //   * a team's range may cover the tail of one sequence, several whole sequences and the
 //     head of another: each such "piece" yields either the final fp16 output (piece ==
 //     whole sequence) or an fp32 partial (normalised output + log2-domain log-sum-exp) in
