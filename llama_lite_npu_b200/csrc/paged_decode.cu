@@ -30,7 +30,9 @@
 // (tokens [16w, 16w+16)) of every tile: S^T = K Q^T and O^T += V^T P^T run on mma.sync
 // m16n8k16 (fp16 in, fp32 accumulate) with the tokens as the M rows and the G query heads as
 // the N columns; per-warp online-softmax states are merged through shared memory at the end
-// of a piece.  No CTA-wide barrier in the steady state; every wait is time-bounded.
+// of a piece (two named barriers among the four consumer warps; the next sequence's Q is
+// requested before the merge so that its latency hides under it).  No CTA-wide barrier in the
+// steady state; every mbarrier wait is time-bounded.
 // The kernel is HBM-bound: algorithmic bytes per token per KV head = 2 (K,V) * 128 * 2 B.
 #include "common.cuh"
 #include "launch.h"
@@ -267,8 +269,6 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const uint32_t stage_base = smem_u32(stages);
   const uint32_t bar_full = smem_u32(bars);                 // [STAGES]
   const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
-  const uint32_t bar_merge_ready = bar_empty + 8 * STAGES;  // consumers wrote their partial state
-  const uint32_t bar_merge_free = bar_merge_ready + 8;      // consumers finished reading it
   if ((stage_base & 1023u) != 0) {  // the swizzled TMA boxes need 1024-byte aligned stages
     set_status(p.status, B200KV_DEV_BAD_PAGE);
     return;
@@ -279,8 +279,6 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
       mbar_init(bar_full + 8 * i, 1);
       mbar_init(bar_empty + 8 * i, kConsumerWarps);
     }
-    mbar_init(bar_merge_ready, kConsumerWarps);
-    mbar_init(bar_merge_free, kConsumerWarps);
     fence_barrier_init();
   }
 
@@ -459,8 +457,27 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const int fcol = (lane & 3) * 2;   // fragment column pair: head within the N block
   const int mi = lane >> 3;          // which 8x8 matrix of an ldmatrix.x4 this lane addresses
   const int lrow = lane & 7;
-  int n_merge = 0;
   pdl_wait_then_trigger();  // q, the workspace and out belong to earlier kernels until here
+
+  // Q of one sequence as B fragments.  The next sequence's Q is requested when a piece ends, so
+  // that its latency hides under the merge of that piece instead of in front of the next tile.
+  uint32_t qn[NB][8][2];
+  int qn_b = -1;
+  auto load_q = [&](int b, uint32_t (&dst)[NB][8][2]) {
+    const __half* qb = p.q + static_cast<int64_t>(b) * p.q_stride_b +
+                       static_cast<int64_t>(head) * p.group * p.q_stride_h + fcol;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int hq = nb * 8 + frow;  // B fragment column n = lane / 4
+      const bool hok = hq < p.group;
+      const __half* qh = qb + static_cast<int64_t>(hq) * p.q_stride_h;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        dst[nb][ks][0] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16)) : 0u;
+        dst[nb][ks][1] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16 + 8)) : 0u;
+      }
+    }
+  };
 
   Tile t;
   for (int it = 0; cons.next(p, t); ++it) {
@@ -469,20 +486,21 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
       for (int j = 0; j < 8; ++j)
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) o[j][nb][0] = o[j][nb][1] = o[j][nb][2] = o[j][nb][3] = 0.f;
-      const __half* qb = p.q + static_cast<int64_t>(t.b) * p.q_stride_b +
-                         static_cast<int64_t>(head) * p.group * p.q_stride_h + fcol;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
         m_run[nb][0] = m_run[nb][1] = -INFINITY;
         l_run[nb][0] = l_run[nb][1] = 0.f;
-        const int hq = nb * 8 + frow;  // B fragment column n = lane / 4
-        const bool hok = hq < p.group;
-        const __half* qh = qb + static_cast<int64_t>(hq) * p.q_stride_h;
+      }
+      if (qn_b == t.b) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          qf[nb][ks][0] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16)) : 0u;
-          qf[nb][ks][1] = hok ? __ldg(reinterpret_cast<const uint32_t*>(qh + ks * 16 + 8)) : 0u;
-        }
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            qf[nb][ks][0] = qn[nb][ks][0];
+            qf[nb][ks][1] = qn[nb][ks][1];
+          }
+      } else {
+        load_q(t.b, qf);
       }
     }
 
@@ -578,10 +596,17 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
 
     if (t.last) {
       // ---- merge the four warps' (m, l, O) and emit the piece --------------------------------
-      if (n_merge > 0 && !mbar_wait_bounded(bar_merge_free, (n_merge - 1) & 1)) {
-        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-        return;
+      if (cons.flat < cons.flat_end) {   // another piece follows: it starts the next non-empty sequence
+        int nb_seq = t.b + 1;
+        while (nb_seq < p.batch && pages_of(seq_len_checked(p, nb_seq)) == 0) ++nb_seq;
+        if (nb_seq < p.batch) {
+          load_q(nb_seq, qn);
+          qn_b = nb_seq;
+        }
       }
+      // the merge buffer is shared by the four consumer warps: named barrier 1 (128 threads)
+      // before it is rewritten and again before it is read
+      asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory");
       float* mo = merge_o + warp * kD * ROWS;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
@@ -605,12 +630,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
               make_float2(o[j][nb][2], o[j][nb][3]);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_merge_ready);
-      if (!mbar_wait_bounded(bar_merge_ready, n_merge & 1)) {
-        set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-        return;
-      }
+      asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory");
       const int64_t slot = (static_cast<int64_t>(team) + t.b) * p.kv_heads + head;
       for (int r = 0; r < p.group; ++r) {
         float mw[kConsumerWarps], M = -INFINITY;
@@ -635,9 +655,6 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
           if (tid == 0) p.part_lse[slot * ROWS + r] = M + log2f(L);
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_merge_free);
-      ++n_merge;
     }
   }
 }
