@@ -632,27 +632,55 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
       }
       asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory");
       const int64_t slot = (static_cast<int64_t>(team) + t.b) * p.kv_heads + head;
-      for (int r = 0; r < p.group; ++r) {
-        float mw[kConsumerWarps], M = -INFINITY;
+      // Thread = output column; its ROWS values of a warp's O are contiguous in the merge buffer
+      // (vector loads), the (m, l) pairs are broadcast loads, and all rows are merged in registers.
+#pragma unroll 1
+      for (int r0 = 0; r0 < ROWS; r0 += 8) {   // eight rows at a time keeps the registers modest
+        float M[8], L[8], acc[8];
+        float mw[kConsumerWarps][8], lw[kConsumerWarps][8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          M[r] = -INFINITY;
+          L[r] = acc[r] = 0.f;
+        }
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
-          mw[w] = merge_ml[(w * ROWS + r) * 2];
-          M = fmaxf(M, mw[w]);
+#pragma unroll
+          for (int r2 = 0; r2 < 4; ++r2) {
+            const float4 v = *reinterpret_cast<const float4*>(merge_ml + (w * ROWS + r0 + 2 * r2) * 2);
+            mw[w][2 * r2] = v.x;
+            lw[w][2 * r2] = v.y;
+            mw[w][2 * r2 + 1] = v.z;
+            lw[w][2 * r2 + 1] = v.w;
+            M[2 * r2] = fmaxf(M[2 * r2], v.x);
+            M[2 * r2 + 1] = fmaxf(M[2 * r2 + 1], v.z);
+          }
         }
-        float L = 0.f, acc = 0.f;
 #pragma unroll
         for (int w = 0; w < kConsumerWarps; ++w) {
-          const float sc = (mw[w] == -INFINITY) ? 0.f : fast_exp2(mw[w] - M);
-          L += sc * merge_ml[(w * ROWS + r) * 2 + 1];
-          acc += sc * merge_o[(w * kD + tid) * ROWS + r];
+          const float4 v0 = *reinterpret_cast<const float4*>(merge_o + (w * kD + tid) * ROWS + r0);
+          const float4 v1 = *reinterpret_cast<const float4*>(merge_o + (w * kD + tid) * ROWS + r0 + 4);
+          const float ov[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float sc = (mw[w][r] == -INFINITY) ? 0.f : fast_exp2(mw[w][r] - M[r]);
+            L[r] += sc * lw[w][r];
+            acc[r] += sc * ov[r];
+          }
         }
-        const float val = acc / L;
-        if (t.whole) {
-          p.out[static_cast<int64_t>(t.b) * p.out_stride_b +
-                (static_cast<int64_t>(head) * p.group + r) * p.out_stride_h + tid] = __float2half_rn(val);
-        } else {
-          p.part_o[(slot * ROWS + r) * kD + tid] = val;
-          if (tid == 0) p.part_lse[slot * ROWS + r] = M + log2f(L);
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          if (r0 + r < p.group) {
+            const float val = acc[r] / L[r];
+            if (t.whole) {
+              p.out[static_cast<int64_t>(t.b) * p.out_stride_b +
+                    (static_cast<int64_t>(head) * p.group + r0 + r) * p.out_stride_h + tid] =
+                  __float2half_rn(val);
+            } else {
+              p.part_o[(slot * ROWS + r0 + r) * kD + tid] = val;
+              if (tid == 0) p.part_lse[slot * ROWS + r0 + r] = M[r] + log2f(L[r]);
+            }
+          }
         }
       }
     }
