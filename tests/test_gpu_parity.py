@@ -461,3 +461,20 @@ def test_prefill_tile_pairs_odd_even_counts(group, kvh):
     c = W.make_prefill_case(cfg, fill="hash", prompt_lens=prompts, shared_pages=shared)
     got, _ = _prefill_gpu(c, "block")
     assert _maxdiff(got, _prefill_oracle(c)) <= ATTN_TOL
+
+
+@pytest.mark.parametrize("kvh,heads", [(8, 16), (1, 8)])
+def test_decode_many_short_sequences_unit_partition(kvh, heads):
+    """Hundreds of short and empty sequences with a few long ones: the page line is cut in units
+    that charge every sequence start, so cuts snap to sequence starts, some teams end many pieces
+    and some ranges are empty; every row must still equal the oracle."""
+    rng = np.random.default_rng(5)
+    lens = rng.integers(0, 40, size=300)
+    lens[::37] = rng.integers(500, 3000, size=len(lens[::37]))
+    lens[5] = 0
+    cfg = W.DecodeConfig("short_mix", len(lens), heads, kvh, 4096, 1, 1, seed=84)
+    c = W.make_decode_case(cfg, fill="hash", lengths=lens)
+    got = _decode_gpu(c, "block")
+    want = O.paged_decode(c.q, c.k_cache, c.v_cache, SCALE, c.token_table, c.seq_lens_t)
+    assert _maxdiff(got, want) <= ATTN_TOL
+    assert float(got[5].abs().sum()) == 0.0
