@@ -534,8 +534,11 @@ def run_prefill(args, cfg_full):
     if rank == 0:
         peak_file = ROOT / "MEASURED_PEAKS.json"
         peak, kind = 1590.0, "fallback"
+        sustained = None
         if peak_file.exists():
-            peak, kind = float(json.loads(peak_file.read_text())["bf16_tflops"]), "measured (burst)"
+            peaks = json.loads(peak_file.read_text())
+            peak, kind = float(peaks["bf16_tflops"]), "measured (burst)"
+            sustained = peaks.get("bf16_tflops_sustained")
         achieved = flops / (ms_kernel * 1e-3) / 1e12
         line = {
             "metric": "paged_prefill_tensor_throughput", "value": float(tot.item()) / (ms_step * 1e-3) / 1e12,
@@ -551,7 +554,11 @@ def run_prefill(args, cfg_full):
             "flops_per_step": float(tot.item()),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "peak_source": f"of {kind}",
-                         "kernel": "paged_prefill_kernel", "us_per_launch": ms_kernel * 1e3, "traffic": None},
+                         "kernel": "paged_prefill_kernel", "us_per_launch": ms_kernel * 1e3, "traffic": None,
+                         # the timed region is seconds of back-to-back tensor work when --steps is
+                         # large: the power-capped (sustained) cuBLAS figure is given beside the burst one
+                         "peak_sustained": sustained,
+                         "frac_of_sustained": (achieved / float(sustained)) if sustained else None},
             "e2e": {"value": float(tot.item()) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": (h_q.numel() + h_kv.numel()) * 2 * world,
                     "d2h_bytes_per_step": h_out.numel() * 2 * world},
