@@ -1,20 +1,25 @@
 """Benchmark of the paged-KV decode step (KV append + paged flash-decoding).
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c5|c1] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c5|c1|c4] [--impl reference]
 
 A "step" is one decode step of one transformer layer over the whole batch: scatter the
 step's new K/V rows into the page pool by slot_mapping, then attend every sequence's single
-query token to its paged context.  The default workload is the Qwen3-32B shape (batch 32, 64
-Q / 8 KV heads, head_dim 128, page_size 16, context lengths uniform in [1024, 4096], 65536-page
-shuffled pool).  With N > 1 (launched by torchrun, one rank per GPU) the KV heads are sharded
-over the ranks — same sequences, 8/N KV heads each — which needs no collective in the path;
-torch.distributed is used only for the timing barrier and the max-over-ranks reduction.
+query token to its paged context (one fused launch).  The default workload is the Qwen3-32B
+shape (batch 32, 64 Q / 8 KV heads, head_dim 128, page_size 16, context lengths uniform in
+[1024, 4096], 65536-page shuffled pool).  With N > 1 (launched by torchrun, one rank per GPU)
+the KV heads are sharded over the ranks — same sequences, 8/N KV heads each — which needs no
+collective in the path; torch.distributed is used only for the timing barrier and the
+max-over-ranks reduction.
 
 Prints ONE JSON line (rank 0).  ``value`` is algorithmic HBM traffic of the whole job per
 second with all inputs resident in HBM (CUDA-graph replay, device-timed); ``e2e`` is the
 same metric through the Python operator API with the step's inputs copied from pinned host
-memory and the result copied back inside the timed region.  ``--impl reference`` times the
-CPU torch statement of the same path (the oracle port) on the host cores instead.
+memory and the result copied back inside the timed region; ``check`` is the max-abs-error of
+a few sequences of the benchmarked run's own output against the CPU oracle (untimed); at one
+GPU ``secondary`` carries the other benchmark configurations (30B-A3B decode, the long mixed
+decode on its full 2^20-page pool, packed prefill), timed the same way outside the headline
+region.  ``--impl reference`` times the CPU torch statement of the same path (the oracle port)
+on the host cores instead.
 """
 
 from __future__ import annotations
@@ -40,11 +45,17 @@ from llama_lite_npu_b200 import workloads as W  # noqa: E402
 
 METRIC = "paged_decode_hbm_throughput"
 UNIT = "GB/s"
+PREFILL_METRIC = "paged_prefill_tensor_throughput"
 L2_BYTES = 126 * 1024 * 1024
 GRAPH_STEPS = 64   # layer steps captured per CUDA graph (a 64-layer model's decode pass)
+ATTN_TOL = 2e-3
+LOG2E = 1.4426950408889634
 # "c2s" is the C2 shape on a 1 GiB pool: small enough for multi-pass ncu captures.
 C2_SMALL_POOL = W.DecodeConfig("c2_qwen3_32b_decode_smallpool", 32, 64, 8, 16384, 1024, 4096, seed=1002)
 WORKLOADS = {"c1": W.C1, "c2": W.C2, "c2s": C2_SMALL_POOL, "c3": W.C3, "c4": W.C4, "c5": W.C5}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, as "workload bytes"
+# lines written by the profiling pass
+TRAFFIC_FILE = ROOT / "profiles" / "ncu_dram_traffic.txt"
 
 
 def dist_env():
@@ -56,10 +67,25 @@ def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            d = json.loads(p.read_text())
+            return {"hbm": float(d["hbm_gbs"]), "tensor": float(d["bf16_tflops"]),
+                    "tensor_sustained": d.get("bf16_tflops_sustained"), "kind": "measured"}
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return {"hbm": 6650.0, "tensor": 1590.0, "tensor_sustained": 1400.0, "kind": "fallback"}
+
+
+def ncu_traffic(workload: str, world: int):
+    if world != 1 or not TRAFFIC_FILE.exists():
+        return None
+    for line in TRAFFIC_FILE.read_text().splitlines():
+        parts = line.split()
+        if len(parts) >= 2 and parts[0] == workload:
+            try:
+                return float(parts[1])
+            except ValueError:
+                return None
+    return None
 
 
 # ------------------------------------------------------------------------------------------
@@ -71,7 +97,7 @@ class ClockSampler:
         0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
     }
 
-    def __init__(self, index: int, period_s: float = 0.01):
+    def __init__(self, index: int, period_s: float = 0.005):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._active = threading.Event()
@@ -115,11 +141,41 @@ class ClockSampler:
         if self._thread is not None:
             self._thread.join(timeout=1.0)
 
-    def summary(self):
+    def summary(self, reset: bool = False):
         if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+            out = {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        else:
+            out = {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                   "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        if reset:
+            self.samples, self.reasons = [], set()
+        return out
+
+
+# ------------------------------------------------------------------------------------------
+# configuration echo: identical in the GPU arm and the CPU arm
+# ------------------------------------------------------------------------------------------
+def workload_config(cfg):
+    if isinstance(cfg, W.PrefillConfig):
+        return {
+            "workload": cfg.name, "batch": cfg.batch, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads,
+            "head_dim": cfg.head_dim, "page_size": cfg.page_size, "num_pages": cfg.num_pages,
+            "prompt_lengths": f"uniform[{cfg.prompt_lo},{cfg.prompt_hi}]",
+            "shared_prefix_pages": f"0-{int(cfg.shared_frac_hi * 100)}% of each prompt",
+            "step": "kv_append(suffix tokens) + paged causal prefill",
+            "parallelism": "kv-head shards over the GPUs, no collective",
+            "l2": "L2 flushed by the step itself: q + out + new K/V (>200 MB) stream through every step",
+        }
+    return {
+        "workload": cfg.name, "batch": cfg.batch, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads,
+        "head_dim": cfg.head_dim, "page_size": cfg.page_size, "num_pages": cfg.num_pages,
+        "context_lengths": f"{cfg.len_dist}[{cfg.len_lo},{cfg.len_hi}]",
+        "step": "kv_append(1 token/seq) + paged flash-decoding",
+        "parallelism": ("request shards over the GPUs, no collective" if cfg.name.startswith("c3")
+                        else "kv-head shards over the GPUs, no collective"),
+        "l2": (f"inputs larger than L2: consecutive steps visit different layer pools round-robin, at least "
+               f"2.5 x {L2_BYTES >> 20} MiB of K/V traffic before a byte repeats"),
+    }
 
 
 # ------------------------------------------------------------------------------------------
@@ -143,16 +199,6 @@ def cpu_step(case) -> None:
                    case.token_table, case.seq_lens_t)
 
 
-def time_cpu(case, steps: int, warmup: int):
-    for _ in range(warmup):
-        cpu_step(case)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_step(case)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return dt, step_bytes(case) / dt / 1e9
-
-
 def step_bytes(case) -> int:
     """Algorithmic bytes of one step: decode traffic + the append's read, write and slots."""
     c = case.cfg
@@ -160,10 +206,67 @@ def step_bytes(case) -> int:
     return case.algorithmic_bytes() + append
 
 
-def cpu_sample_size(cfg) -> int:
-    # sized for roughly 10-30 s of CPU work over the few repetitions made
-    return {"c2_qwen3_32b_decode": 16, "c3_qwen3_30b_a3b_decode": 16, "c5_long_mixed_decode": 16}.get(
-        cfg.name, cfg.batch)
+def cpu_decode_baseline(cfg, steps: int, warmup: int, budget_s: float):
+    """Time the oracle's decode step on as many of the workload's first sequences as fit the
+    budget.  Returns (seconds per sample step, GB/s, sequences used, steps, warm-ups)."""
+    probe = cpu_sample_case(cfg, min(2, cfg.batch))
+    cpu_step(probe)
+    t0 = time.perf_counter()
+    cpu_step(probe)
+    per_seq = (time.perf_counter() - t0) / probe.cfg.batch
+    n = int(max(1, min(cfg.batch, budget_s / max(per_seq, 1e-6) / max(steps + warmup, 1))))
+    case = cpu_sample_case(cfg, n)
+    for _ in range(warmup):
+        cpu_step(case)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_step(case)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return dt, step_bytes(case) / dt / 1e9, n
+
+
+def cpu_prefill_case(cfg: W.PrefillConfig, n_req: int):
+    """The ``n_req`` shortest requests of the workload (same drawn lengths and prefix hits) in a
+    compact pool."""
+    lens, shared = W.draw_prefill_lengths(cfg)
+    order = np.argsort(lens, kind="stable")[:n_req]
+    pages = int(((lens[order] + cfg.page_size - 1) // cfg.page_size).sum())
+    sub = W.PrefillConfig(cfg.name + "_cpu_sample", len(order), cfg.q_heads, cfg.kv_heads, pages,
+                          cfg.prompt_lo, cfg.prompt_hi, cfg.shared_frac_hi, cfg.head_dim, cfg.page_size, cfg.seed)
+    return W.make_prefill_case(sub, device="cpu", fill="hash", prompt_lens=lens[order], shared_pages=shared[order])
+
+
+def cpu_prefill_step(case) -> None:
+    from oracle import paged_kv_oracle as O
+
+    kvh = case.cfg.kv_heads
+    O.kv_append(case.new_kv, case.slots, case.pool)
+    O.paged_attention(case.q, case.pool[:, :kvh], case.pool[:, kvh:], 1.0 / math.sqrt(case.cfg.head_dim),
+                      case.token_table, case.req_ids, case.q_start, case.ctx_lens_t, case.q_lens_t)
+
+
+def cpu_prefill_baseline(cfg, steps: int, warmup: int, budget_s: float):
+    """Oracle prefill on the workload's shortest ``n`` requests that fit the budget.  Returns
+    (seconds per sample step, TFLOP/s, requests used)."""
+    probe = cpu_prefill_case(cfg, 1)
+    t0 = time.perf_counter()
+    cpu_prefill_step(probe)
+    rate = probe.flops() / max(time.perf_counter() - t0, 1e-6)      # flop/s on the smallest request
+    lens, shared = W.draw_prefill_lengths(cfg)
+    order = np.argsort(lens, kind="stable")
+    ctx = (shared[order] * cfg.page_size).astype(np.int64)
+    q = lens[order].astype(np.int64) - ctx
+    cum = np.cumsum(4 * cfg.head_dim * cfg.q_heads * (q * ctx + q * (q + 1) // 2))
+    allowed = rate * budget_s / max(steps + warmup, 1)
+    n = int(max(1, min(cfg.batch, np.searchsorted(cum, allowed, side="right"))))
+    case = probe if n == 1 else cpu_prefill_case(cfg, n)
+    for _ in range(warmup):
+        cpu_prefill_step(case)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu_prefill_step(case)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return dt, case.flops() / dt / 1e12, n
 
 
 def run_reference(args, cfg_full):
@@ -172,60 +275,90 @@ def run_reference(args, cfg_full):
         return
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    n = min(cfg_full.batch, cpu_sample_size(cfg_full))
-    case = cpu_sample_case(cfg_full, n)
-    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
-    dt, gbs = time_cpu(case, steps, warmup)
-    sample = (f"first {n} of {cfg_full.batch} sequences, all {cfg_full.q_heads} Q heads, "
-              f"{steps} timed steps after {warmup} warm-up; value = sample bytes / sample time")
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    if isinstance(cfg_full, W.PrefillConfig):
+        dt, rate, n = cpu_prefill_baseline(cfg_full, steps, warmup, budget_s=150.0)
+        metric, unit = PREFILL_METRIC, "TFLOP/s"
+        sample = (f"the {n} shortest of {cfg_full.batch} requests, all {cfg_full.q_heads} Q heads, {steps} timed "
+                  f"steps after {warmup} warm-up; value = sample flops / sample time")
+    else:
+        dt, rate, n = cpu_decode_baseline(cfg_full, steps, warmup, budget_s=150.0)
+        metric, unit = METRIC, UNIT
+        sample = (f"first {n} of {cfg_full.batch} sequences, all {cfg_full.q_heads} Q heads, {steps} timed "
+                  f"steps after {warmup} warm-up; value = sample bytes / sample time")
     line = {
-        "impl": "reference", "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3 * cfg_full.batch / n,
+        "impl": "reference", "metric": metric, "value": rate, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3 * cfg_full.batch / n,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-        "data": "synthetic", "config": workload_config(cfg_full, args.gpus, None),
-        "cpu_baseline": {"value": gbs, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": gbs, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "data": "synthetic", "config": workload_config(cfg_full),
+        "cpu_baseline": {"value": rate, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def workload_config(cfg, gpus, layers):
-    d = {
-        "workload": cfg.name, "batch": cfg.batch, "q_heads": cfg.q_heads, "kv_heads": cfg.kv_heads,
-        "head_dim": cfg.head_dim, "page_size": cfg.page_size, "num_pages": cfg.num_pages,
-        "context_lengths": f"{cfg.len_dist}[{cfg.len_lo},{cfg.len_hi}]",
-        "step": "kv_append(1 token/seq) + paged flash-decoding",
-        "parallelism": f"kv-head shards over {gpus} GPU(s), no collective",
-    }
-    if layers is not None:
-        d["l2"] = (f"inputs larger than L2: {layers} layer pools visited round-robin, so no K/V byte "
-                   f"is re-read within {L2_BYTES >> 20} MiB of traffic")
-    return d
-
-
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
-def run_b200(args, cfg_full):
-    from llama_lite_npu_b200 import _lib, kernels
+class Timer:
+    """CUDA-graph capture + event timing on one stream, barrier + synchronize on both sides."""
 
-    rank, local_rank, world = dist_env()
-    if world != args.gpus and world != 1:
-        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (use --impl reference for the CPU arm)")
-    _lib.lib()
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    if world > 1:
-        import torch.distributed as dist
+    def __init__(self, stream, barrier):
+        self.stream, self.barrier = stream, barrier
 
-        dist.init_process_group("nccl", device_id=torch.device(dev))
-    cfg, parallelism = W.shard_config(cfg_full, world, rank)
+    def capture(self, fn, n):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=self.stream):
+            for i in range(n):
+                fn(i)
+        return g
+
+    def run(self, fn, k, per_graph=GRAPH_STEPS):
+        """Milliseconds for exactly k steps: graphs of up to per_graph consecutive steps."""
+        full, rest = divmod(k, per_graph)
+        g_full = self.capture(fn, per_graph) if full else None
+        g_rest = self.capture(fn, rest) if rest else None
+        for g in (g_full, g_rest):     # untimed replay: first-launch upload of the graph
+            if g is not None:
+                g.replay()
+        self.barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record(self.stream)
+        for _ in range(full):
+            g_full.replay()
+        if g_rest is not None:
+            g_rest.replay()
+        t1.record(self.stream)
+        self.barrier()
+        return t0.elapsed_time(t1)
+
+
+def decode_check(case, pool, out, n_seqs=4):
+    """Max-abs-error of a few sequences of a benchmarked output against the CPU oracle."""
+    from oracle import paged_kv_oracle as O
+
+    b_all = sorted({0, case.cfg.batch // 3, (2 * case.cfg.batch) // 3, case.cfg.batch - 1})[:n_seqs]
+    kvh = case.cfg.kv_heads
+    worst = 0.0
+    for b in b_all:
+        L = int(case.seq_lens[b])
+        sl = case.token_table[b, :L].long()
+        k, v = pool[:, :kvh][sl].cpu(), pool[:, kvh:][sl].cpu()
+        want = O.paged_decode(case.q[b: b + 1].cpu(), k, v, 1.0 / math.sqrt(case.cfg.head_dim),
+                              torch.arange(L, dtype=torch.int32)[None], torch.tensor([L]))
+        worst = max(worst, float((out[b: b + 1].float().cpu() - want.float()).abs().max()))
+    return {"max_abs_err": worst, "sequences": len(b_all), "tolerance": ATTN_TOL, "ok": worst <= ATTN_TOL,
+            "against": "CPU oracle, on the output of the benchmarked step"}
+
+
+def decode_bench(cfg, dev, steps, warmup, timer, prologue=False, with_e2e=True):
+    """Device-time the decode step of one (sharded) configuration.  Returns a dict of figures."""
+    from llama_lite_npu_b200 import kernels
+
     scale = 1.0 / math.sqrt(cfg.head_dim)
     kvh = cfg.kv_heads
-
+    stream = timer.stream
     # One case gives tables, lengths, q and the new rows; the pool is replicated per "layer".
     case = W.make_decode_case(cfg, device=dev, fill="randn", fill_pool=False)
     bytes_step = step_bytes(case)
@@ -238,8 +371,9 @@ def run_b200(args, cfg_full):
         g = torch.Generator(device=dev)
         g.manual_seed(cfg.seed * 977 + i)
         p.normal_(generator=g)
+    out = torch.empty_like(case.q)
 
-    if args.prologue:
+    if prologue:
         # the step starts from the raw projections: QK-RMSNorm + rotary embedding + append, fused
         g = torch.Generator(device=dev)
         g.manual_seed(cfg.seed + 5)
@@ -252,13 +386,165 @@ def run_b200(args, cfg_full):
 
     def step(i):
         pool = pools[i % layers]
-        if args.prologue:
+        if prologue:
             kernels.fused_qk_norm_rope_append(raw_q, raw_kv, norm_w[0], norm_w[1], 1e-6, cos, sin,
                                               case.slots, pool, out=case.q)
+            kernels.flash_decoding(case.q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
+                                   case.seq_lens_t, case.max_len, table_kind="block", out=out)
         else:
-            kernels.update_kv_buffer(case.new_kv, case.slots, pool)
-        return kernels.flash_decoding(case.q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
-                                      case.seq_lens_t, case.max_len, table_kind="block")
+            kernels.append_flash_decoding(case.new_kv, case.slots, pool, case.q, scale, case.block_table,
+                                          case.seq_lens_t, case.max_len, table_kind="block", out=out)
+
+    def decode_only(i):
+        pool = pools[i % layers]
+        kernels.flash_decoding(case.q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
+                               case.seq_lens_t, case.max_len, table_kind="block", out=out)
+
+    res = {"case": case, "bytes_step": bytes_step, "alg_bytes": case.algorithmic_bytes(), "layers": layers,
+           "launches_per_step": 2 if prologue else 1}
+    with torch.cuda.stream(stream):
+        for i in range(max(warmup, 3)):
+            step(i)
+        stream.synchronize()
+        kernels.check_status(torch.device(dev).index)
+        res["check"] = decode_check(case, pools[(max(warmup, 3) - 1) % layers], out)
+        # ---- value: K graph-replayed steps, inputs resident in HBM ---------------------------
+        res["ms_total"] = timer.run(step, steps)
+        # ---- roofline: the decode kernel alone, same events -----------------------------------
+        n_k = max(steps, GRAPH_STEPS)
+        res["ms_kernel"] = timer.run(decode_only, n_k) / n_k
+        if with_e2e:
+            # ---- e2e: operator API, host inputs in, result out, every step ---------------------
+            # The step's host inputs (q, the new K/V rows, slot_mapping, lengths) sit in ONE pinned
+            # staging buffer and cross PCIe in one copy; the result comes back in one copy.
+            parts = [("q", case.q), ("kv", case.new_kv), ("lens", case.seq_lens_t), ("slots", case.slots)]
+            offs, cur = {}, 0
+            for name, t in parts:
+                cur = (cur + 15) // 16 * 16
+                offs[name] = (cur, t.numel() * t.element_size())
+                cur += t.numel() * t.element_size()
+            h_in = torch.empty(cur, dtype=torch.uint8).pin_memory()
+            d_in = torch.empty(cur, dtype=torch.uint8, device=dev)
+
+            def view(buf, name, like):
+                o, n = offs[name]
+                return buf[o:o + n].view(like.dtype).view(like.shape)
+
+            for name, t in parts:
+                view(h_in, name, t).copy_(t.cpu())
+            d_q, d_kv = view(d_in, "q", case.q), view(d_in, "kv", case.new_kv)
+            d_lens, d_slots = view(d_in, "lens", case.seq_lens_t), view(d_in, "slots", case.slots)
+            h_out = torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory()
+            d_out = torch.empty_like(case.q)
+
+            def e2e_step(i):
+                d_in.copy_(h_in, non_blocking=True)
+                kernels.append_flash_decoding(d_kv, d_slots, pools[i % layers], d_q, scale, case.block_table,
+                                              d_lens, case.max_len, table_kind="block", out=d_out)
+                h_out.copy_(d_out, non_blocking=True)
+
+            for i in range(3):
+                e2e_step(i)
+            timer.barrier()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            x0.record(stream)
+            for i in range(steps):
+                e2e_step(i)
+            x1.record(stream)
+            timer.barrier()
+            res["ms_e2e_total"] = x0.elapsed_time(x1)
+            res["h2d"], res["d2h"] = cur, h_out.numel() * h_out.element_size()
+        kernels.check_status(torch.device(dev).index)
+    del pools
+    return res
+
+
+def prefill_bench(cfg, dev, steps, warmup, timer, with_e2e=True):
+    from llama_lite_npu_b200 import kernels
+    from oracle import paged_kv_oracle as O
+
+    kvh = cfg.kv_heads
+    scale_log2 = LOG2E / math.sqrt(cfg.head_dim)
+    case = W.make_prefill_case(cfg, device="cpu", fill="hash")
+    host_q = case.q
+    for name in ("pool", "block_table", "req_ids", "q_start", "ctx_lens_t", "q_lens_t", "q", "new_kv", "slots"):
+        setattr(case, name, getattr(case, name).to(dev))
+    stream = timer.stream
+
+    def attend(_i=0):
+        return kernels.paged_chunk_flash_attention(
+            case.q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
+            case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
+
+    def step(_i=0):
+        kernels.update_kv_buffer(case.new_kv, case.slots, case.pool)
+        return attend()
+
+    res = {"case": case, "flops": case.flops()}
+    with torch.cuda.stream(stream):
+        for _ in range(max(warmup, 3)):
+            got = step()
+        stream.synchronize()
+        kernels.check_status(torch.device(dev).index)
+        # check: the shortest request of the benchmarked output against the oracle
+        r = int(np.argmin(case.prompt_lens))
+        q0, qn, ctx = int(case.q_start[r]), int(case.q_lens[r]), int(case.ctx_lens[r])
+        sl = case.token_table[r, : ctx + qn].long()
+        pool_c = case.pool[sl.to(dev)].cpu()
+        want = O.paged_attention(host_q[q0: q0 + qn], pool_c[:, :kvh], pool_c[:, kvh:], 1.0 / math.sqrt(cfg.head_dim),
+                                 torch.arange(ctx + qn, dtype=torch.int32)[None], torch.zeros(1, dtype=torch.int32),
+                                 torch.zeros(1, dtype=torch.int32), torch.tensor([ctx]), torch.tensor([qn]))
+        err = float((got[q0: q0 + qn].float().cpu() - want.float()).abs().max())
+        res["check"] = {"max_abs_err": err, "requests": 1, "tolerance": ATTN_TOL, "ok": err <= ATTN_TOL,
+                        "against": "CPU oracle, shortest request of the benchmarked output"}
+        res["ms_step"] = timer.run(step, steps, per_graph=1) / steps
+        res["ms_kernel"] = timer.run(attend, steps, per_graph=1) / steps
+        if with_e2e:
+            h_q, h_kv = host_q.pin_memory(), case.new_kv.cpu().pin_memory()
+            h_out = torch.empty_like(h_q).pin_memory()
+            d_q, d_kv = torch.empty_like(case.q), torch.empty_like(case.new_kv)
+
+            def e2e_step():
+                d_q.copy_(h_q, non_blocking=True)
+                d_kv.copy_(h_kv, non_blocking=True)
+                kernels.update_kv_buffer(d_kv, case.slots, case.pool)
+                o = kernels.paged_chunk_flash_attention(
+                    d_q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
+                    case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
+                h_out.copy_(o, non_blocking=True)
+
+            for _ in range(2):
+                e2e_step()
+            timer.barrier()
+            x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            n_e2e = max(3, min(steps, 20))
+            x0.record(stream)
+            for _ in range(n_e2e):
+                e2e_step()
+            x1.record(stream)
+            timer.barrier()
+            res["ms_e2e"] = x0.elapsed_time(x1) / n_e2e
+            res["h2d"], res["d2h"] = (h_q.numel() + h_kv.numel()) * 2, h_out.numel() * 2
+        kernels.check_status(torch.device(dev).index)
+    return res
+
+
+def gpu_setup(args):
+    from llama_lite_npu_b200 import _lib
+
+    rank, local_rank, world = dist_env()
+    if world != args.gpus and world != 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (use --impl reference for the CPU arm)")
+    _lib.lib()
+    torch.cuda.set_device(local_rank)
+    dev = f"cuda:{local_rank}"
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=torch.device(dev))
 
     def barrier():
         torch.cuda.synchronize()
@@ -266,147 +552,91 @@ def run_b200(args, cfg_full):
             dist.barrier()
             torch.cuda.synchronize()
 
+    return rank, local_rank, world, dev, dist, barrier
+
+
+def secondary_lines(dev, timer, sampler, peaks):
+    """The other benchmark configurations at one GPU, a short device-timed run each."""
+    out = {}
+    for key, cfg in (("c3", W.C3), ("c5", W.C5)):
+        sampler.summary(reset=True)
+        with sampler:
+            r = decode_bench(cfg, dev, 40, 3, timer, with_e2e=False)
+        ach = r["alg_bytes"] / (r["ms_kernel"] * 1e-3) / 1e9
+        out[key] = {"workload": cfg.name, "us": r["ms_kernel"] * 1e3, "us_per_step": r["ms_total"] / 40 * 1e3,
+                    "achieved": ach, "unit": "GB/s", "frac": ach / peaks["hbm"], "bound": "hbm",
+                    "bytes_per_launch": r["alg_bytes"], "num_pages": cfg.num_pages, "check": r["check"],
+                    "clocks": sampler.summary(reset=True)}
+        del r
+        torch.cuda.empty_cache()
+    with sampler:
+        r = prefill_bench(W.C4, dev, 40, 3, timer, with_e2e=False)
+    ach = r["flops"] / (r["ms_kernel"] * 1e-3) / 1e12
+    out["c4"] = {"workload": W.C4.name, "us": r["ms_kernel"] * 1e3, "us_per_step": r["ms_step"] * 1e3,
+                 "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tensor"], "bound": "tensor",
+                 "flops_per_launch": r["flops"], "check": r["check"], "clocks": sampler.summary(reset=True)}
+    return out
+
+
+def run_b200(args, cfg_full):
+    rank, local_rank, world, dev, dist, barrier = gpu_setup(args)
+    cfg, _ = W.shard_config(cfg_full, world, rank)
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    stream = torch.cuda.Stream()
-    with torch.cuda.stream(stream):
-        for i in range(max(args.warmup, 3)):
-            step(i)
-        stream.synchronize()
-        kernels.check_status(local_rank)
-        # A decode pass of a model is one CUDA graph holding every layer's step back to back, so
-        # the timed region is graphs of up to GRAPH_STEPS consecutive steps (layer pools
-        # visited round-robin), replayed until exactly K steps have run.
-        def capture(fn, n):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                for i in range(n):
-                    fn(i)
-            return g
+    timer = Timer(torch.cuda.Stream(), barrier)
+    if sampler:
+        sampler.__enter__()
+    r = decode_bench(cfg, dev, args.steps, args.warmup, timer, prologue=args.prologue)
+    if sampler:
+        sampler.__exit__()
+    clocks = sampler.summary(reset=True) if sampler else None
 
-        def plan(k):
-            full, rest = divmod(k, GRAPH_STEPS)
-            return full, rest
-
-        def timed(fn, k):
-            full, rest = plan(k)
-            g_full = capture(fn, GRAPH_STEPS) if full else None
-            g_rest = capture(fn, rest) if rest else None
-            for g in (g_full, g_rest):     # untimed replay: first-launch upload of the graph
-                if g is not None:
-                    g.replay()
-            barrier()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record(stream)
-            for _ in range(full):
-                g_full.replay()
-            if g_rest is not None:
-                g_rest.replay()
-            t1.record(stream)
-            barrier()
-            return t0.elapsed_time(t1)
-
-        # ---- value: K graph-replayed steps, inputs resident in HBM ---------------------------
-        if sampler:
-            sampler.__enter__()
-        ms_total = timed(step, args.steps)
-
-        # ---- roofline: the decode kernels alone (split-KV kernel + its merge), same events ----
-        out = torch.empty_like(case.q)
-
-        def decode_only(i):
-            pool = pools[i % layers]
-            kernels.flash_decoding(case.q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
-                                   case.seq_lens_t, case.max_len, table_kind="block", out=out)
-
-        n_k = max(args.steps, GRAPH_STEPS)
-        ms_kernel = timed(decode_only, n_k) / n_k
-
-        # ---- e2e: operator API, host inputs in, result out, every step -----------------------
-        # The step's host inputs (q, the new K/V rows, slot_mapping, lengths) sit in ONE pinned
-        # staging buffer and cross PCIe in one copy; the result comes back in one copy.
-        parts = [("q", case.q), ("kv", case.new_kv), ("lens", case.seq_lens_t), ("slots", case.slots)]
-        offs, cur = {}, 0
-        for name, t in parts:
-            cur = (cur + 15) // 16 * 16
-            offs[name] = (cur, t.numel() * t.element_size())
-            cur += t.numel() * t.element_size()
-        h_in = torch.empty(cur, dtype=torch.uint8).pin_memory()
-        d_in = torch.empty(cur, dtype=torch.uint8, device=dev)
-
-        def view(buf, name, like):
-            o, n = offs[name]
-            return buf[o:o + n].view(like.dtype).view(like.shape)
-
-        for name, t in parts:
-            view(h_in, name, t).copy_(t.cpu())
-        d_q, d_kv = view(d_in, "q", case.q), view(d_in, "kv", case.new_kv)
-        d_lens, d_slots = view(d_in, "lens", case.seq_lens_t), view(d_in, "slots", case.slots)
-        h_out = torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory()
-        h2d = cur
-        d2h = h_out.numel() * h_out.element_size()
-
-        def e2e_step(i):
-            pool = pools[i % layers]
-            d_in.copy_(h_in, non_blocking=True)
-            kernels.update_kv_buffer(d_kv, d_slots, pool)
-            o = kernels.flash_decoding(d_q, pool[:, :kvh], pool[:, kvh:], scale, case.block_table,
-                                       d_lens, case.max_len, table_kind="block")
-            h_out.copy_(o, non_blocking=True)
-
-        for i in range(3):
-            e2e_step(i)
-        barrier()
-        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        x0.record(stream)
-        for i in range(args.steps):
-            e2e_step(i)
-        x1.record(stream)
-        barrier()
-        ms_e2e_total = x0.elapsed_time(x1)
-        if sampler:
-            sampler.__exit__()
-        kernels.check_status(local_rank)
-
-    times = torch.tensor([ms_total, ms_e2e_total, ms_kernel], dtype=torch.float64, device=dev)
-    total_bytes = torch.tensor([float(bytes_step)], dtype=torch.float64, device=dev)
+    times = torch.tensor([r["ms_total"], r["ms_e2e_total"], r["ms_kernel"]], dtype=torch.float64, device=dev)
+    total_bytes = torch.tensor([float(r["bytes_step"])], dtype=torch.float64, device=dev)
+    ok = torch.tensor([1.0 if r["check"]["ok"] else 0.0, r["check"]["max_abs_err"]], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(total_bytes, op=dist.ReduceOp.SUM)
+        dist.all_reduce(ok, op=dist.ReduceOp.MAX)     # worst error over ranks (and "ok" of rank 0 kept below)
     ms_total, ms_e2e_total, ms_kernel = times.tolist()
     job_bytes = float(total_bytes.item())
 
     if rank == 0:
-        peak, peak_kind = measured_peaks()
+        peaks = measured_peaks()
         ms_step = ms_total / args.steps
         value = job_bytes / (ms_step * 1e-3) / 1e9
         e2e_value = job_bytes / (ms_e2e_total / args.steps * 1e-3) / 1e9
-        achieved = case.algorithmic_bytes() / (ms_kernel * 1e-3) / 1e9   # this rank's kernel
+        achieved = r["alg_bytes"] / (ms_kernel * 1e-3) / 1e9   # this rank's kernel
+        check = dict(r["check"], max_abs_err=float(ok[1].item()), ok=float(ok[1].item()) <= ATTN_TOL)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
+            "warmup": args.warmup, "ms_per_step": ms_step, "us_per_step": ms_step * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic",
-            "config": dict(workload_config(cfg_full, world, layers), parallelism=parallelism,
-                           **({"step_prologue": "fused QK-RMSNorm + rotary embedding + KV append"}
-                              if args.prologue else {})),
+            "data": "synthetic", "config": workload_config(cfg_full),
+            "warmup_run": max(args.warmup, 3), "layer_pools": r["layers"],
             "bytes_per_step": job_bytes,
             "roofline": {
-                "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                "kernel": "paged_decode_split_kernel (+ decode_combine_kernel, timed together)",
-                "us_per_launch": ms_kernel * 1e3, "bytes_per_launch": case.algorithmic_bytes(),
+                "bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm"], "peak_source": f"of {peaks['kind']}",
+                "kernel": "paged_decode_kernel (split-KV walk + merge of the partials, one launch)",
+                "us_per_launch": ms_kernel * 1e3, "bytes_per_launch": r["alg_bytes"],
                 "traffic": ncu_traffic(cfg_full.name, world),
             },
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d * world,
-                    "d2h_bytes_per_step": d2h * world, "us_per_step": ms_e2e_total / args.steps * 1e3},
-            "gpu_launches": 3 * args.steps,
-            "clocks": sampler.summary() if sampler else None,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["h2d"] * world,
+                    "d2h_bytes_per_step": r["d2h"] * world, "us_per_step": ms_e2e_total / args.steps * 1e3},
+            "gpu_launches": r["launches_per_step"] * args.steps,
+            "check": check,
+            "clocks": clocks,
         }
+        if args.prologue:
+            line["step_prologue"] = "fused QK-RMSNorm + rotary embedding + KV append, then paged decode"
+        del r
+        torch.cuda.empty_cache()
+        if world == 1 and not args.no_secondary and cfg_full.name == W.C2.name:
+            line["secondary"] = secondary_lines(dev, timer, sampler, peaks)
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             torch.set_num_threads(threads)
-            n = min(cfg_full.batch, cpu_sample_size(cfg_full))
-            cdt, cgbs = time_cpu(cpu_sample_case(cfg_full, n), 2, 1)
+            cdt, cgbs, n = cpu_decode_baseline(cfg_full, 2, 1, budget_s=15.0)
             line["cpu_baseline"] = {
                 "value": cgbs, "unit": UNIT, "cores": threads, "kind": "port",
                 "sample": f"first {n} of {cfg_full.batch} sequences, all Q heads, 2 timed steps after 1 warm-up",
@@ -419,152 +649,57 @@ def run_b200(args, cfg_full):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernel from
-# the ncu captures summarised under profiles/.  The decode capture ran on the small-pool twin of
-# the Qwen3-32B workload (identical sequences and lengths, so identical traffic).
-NCU_TRAFFIC_BYTES = {
-    "c2_qwen3_32b_decode": 345.7e6,
-    "c2_qwen3_32b_decode_smallpool": 345.7e6,
-}
-
-
-def ncu_traffic(workload: str, world: int):
-    return NCU_TRAFFIC_BYTES.get(workload) if world == 1 else None
-
-
 # ------------------------------------------------------------------------------------------
 # Prefill workload (config C4): suffix KV append + packed causal prefill over paged KV
 # ------------------------------------------------------------------------------------------
 def run_prefill(args, cfg_full):
-    from llama_lite_npu_b200 import _lib, kernels
-
-    rank, local_rank, world = dist_env()
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device")
-    _lib.lib()
-    torch.cuda.set_device(local_rank)
-    dev = f"cuda:{local_rank}"
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device(dev))
+    rank, local_rank, world, dev, dist, barrier = gpu_setup(args)
     cfg = W.shard_kv_heads(cfg_full, world, rank) if world > 1 else cfg_full
-    kvh = cfg.kv_heads
-    scale_log2 = 1.4426950408889634 / math.sqrt(cfg.head_dim)
-    case = W.make_prefill_case(cfg, device="cpu", fill="hash")
-    for name in ("pool", "block_table", "req_ids", "q_start", "ctx_lens_t", "q_lens_t", "q", "new_kv", "slots"):
-        setattr(case, name, getattr(case, name).to(dev))
-    flops = case.flops()
-    stream = torch.cuda.Stream()
-
-    def attend():
-        return kernels.paged_chunk_flash_attention(
-            case.q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
-            case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
-
-    def step(_i=0):
-        kernels.update_kv_buffer(case.new_kv, case.slots, case.pool)
-        return attend()
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
-            step()
-        stream.synchronize()
-        kernels.check_status(local_rank)
-
-        def timed(fn, k):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                fn()
-            g.replay()
-            barrier()
-            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            t0.record(stream)
-            for _ in range(k):
-                g.replay()
-            t1.record(stream)
-            barrier()
-            return t0.elapsed_time(t1) / k
-
-        if sampler:
-            sampler.__enter__()
-        ms_step = timed(step, args.steps)
-        ms_kernel = timed(attend, args.steps)
-        h_q, h_kv = case.q.cpu().pin_memory(), case.new_kv.cpu().pin_memory()
-        h_out = torch.empty_like(h_q).pin_memory()
-        d_q, d_kv = torch.empty_like(case.q), torch.empty_like(case.new_kv)
-
-        def e2e_step():
-            d_q.copy_(h_q, non_blocking=True)
-            d_kv.copy_(h_kv, non_blocking=True)
-            kernels.update_kv_buffer(d_kv, case.slots, case.pool)
-            o = kernels.paged_chunk_flash_attention(
-                d_q, case.pool[:, :kvh], case.pool[:, kvh:], scale_log2, case.block_table, case.req_ids,
-                case.q_start, case.ctx_lens_t, case.q_lens_t, case.max_q_len, table_kind="block")
-            h_out.copy_(o, non_blocking=True)
-
-        for _ in range(2):
-            e2e_step()
-        barrier()
-        x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_e2e = max(3, min(args.steps, 20))
-        x0.record(stream)
-        for _ in range(n_e2e):
-            e2e_step()
-        x1.record(stream)
-        barrier()
-        ms_e2e = x0.elapsed_time(x1) / n_e2e
-        if sampler:
-            sampler.__exit__()
-        kernels.check_status(local_rank)
-
-    times = torch.tensor([ms_step, ms_e2e, ms_kernel], dtype=torch.float64, device=dev)
-    tot = torch.tensor([float(flops)], dtype=torch.float64, device=dev)
+    timer = Timer(torch.cuda.Stream(), barrier)
+    if sampler:
+        sampler.__enter__()
+    r = prefill_bench(cfg, dev, args.steps, args.warmup, timer)
+    if sampler:
+        sampler.__exit__()
+    times = torch.tensor([r["ms_step"], r["ms_e2e"], r["ms_kernel"]], dtype=torch.float64, device=dev)
+    tot = torch.tensor([float(r["flops"])], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
     ms_step, ms_e2e, ms_kernel = times.tolist()
     if rank == 0:
-        peak_file = ROOT / "MEASURED_PEAKS.json"
-        peak, kind = 1590.0, "fallback"
-        sustained = None
-        if peak_file.exists():
-            peaks = json.loads(peak_file.read_text())
-            peak, kind = float(peaks["bf16_tflops"]), "measured (burst)"
-            sustained = peaks.get("bf16_tflops_sustained")
-        achieved = flops / (ms_kernel * 1e-3) / 1e12
+        peaks = measured_peaks()
+        sustained = peaks["tensor_sustained"]
+        achieved = r["flops"] / (ms_kernel * 1e-3) / 1e12
         line = {
-            "metric": "paged_prefill_tensor_throughput", "value": float(tot.item()) / (ms_step * 1e-3) / 1e12,
-            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "metric": PREFILL_METRIC, "value": float(tot.item()) / (ms_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f16", "data": "synthetic",
-            "config": {"workload": cfg_full.name, "batch": cfg_full.batch, "q_heads": cfg_full.q_heads,
-                       "kv_heads": cfg_full.kv_heads, "head_dim": 128, "page_size": 16,
-                       "prompt_lengths": f"uniform[{cfg_full.prompt_lo},{cfg_full.prompt_hi}]",
-                       "shared_prefix_pages": "0-50% of each prompt", "total_query_tokens": int(case.q_lens.sum()),
-                       "step": "kv_append(suffix tokens) + paged causal prefill",
-                       "l2": "L2 flushed by the step itself: q + out + new K/V (>200 MB) stream through every step"},
-            "flops_per_step": float(tot.item()),
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "peak_source": f"of {kind}",
-                         "kernel": "paged_prefill_kernel", "us_per_launch": ms_kernel * 1e3, "traffic": None,
+            "dtype": "f16", "data": "synthetic", "config": workload_config(cfg_full),
+            "total_query_tokens": int(r["case"].q_lens.sum()), "flops_per_step": float(tot.item()),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["tensor"], "peak_source": f"of {peaks['kind']} (burst)",
+                         "kernel": "paged_prefill_kernel", "us_per_launch": ms_kernel * 1e3,
+                         "traffic": ncu_traffic(cfg_full.name, world),
                          # the timed region is seconds of back-to-back tensor work when --steps is
                          # large: the power-capped (sustained) cuBLAS figure is given beside the burst one
                          "peak_sustained": sustained,
                          "frac_of_sustained": (achieved / float(sustained)) if sustained else None},
             "e2e": {"value": float(tot.item()) / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "h2d_bytes_per_step": (h_q.numel() + h_kv.numel()) * 2 * world,
-                    "d2h_bytes_per_step": h_out.numel() * 2 * world},
+                    "h2d_bytes_per_step": r["h2d"] * world, "d2h_bytes_per_step": r["d2h"] * world},
             "gpu_launches": 2 * args.steps,
+            "check": r["check"],
             "clocks": sampler.summary() if sampler else None,
         }
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            torch.set_num_threads(threads)
+            cdt, ctf, n = cpu_prefill_baseline(cfg_full, 1, 0, budget_s=25.0)
+            line["cpu_baseline"] = {
+                "value": ctf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"the {n} shortest of {cfg_full.batch} requests, all Q heads, one timed step",
+            }
         print(json.dumps(line))
     if sampler:
         sampler.close()
@@ -581,17 +716,17 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-secondary", action="store_true",
+                    help="skip the short runs of the other configurations that a one-GPU c2 run appends")
     ap.add_argument("--prologue", action="store_true",
                     help="decode workloads: start each step from raw projections (fused QK-RMSNorm + "
-                         "rotary embedding + KV append) instead of the plain KV append")
+                         "rotary embedding + KV append) instead of the append fused into the decode launch")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
-    if isinstance(cfg, W.PrefillConfig):
-        if args.impl == "reference":
-            raise SystemExit("--impl reference times the decode workloads; see tests for the prefill oracle")
-        run_prefill(args, cfg)
-    elif args.impl == "reference":
+    if args.impl == "reference":
         run_reference(args, cfg)
+    elif isinstance(cfg, W.PrefillConfig):
+        run_prefill(args, cfg)
     else:
         run_b200(args, cfg)
 

@@ -12,20 +12,25 @@
  * b200kv_strerror() turns a code into text.  Arguments are validated on the
  * host BEFORE anything is launched, so a non-zero return means nothing ran.
  *
- * Device-side index checks: kernels bounds-check every slot / page id they
- * read from device memory.  An out-of-range index is never dereferenced; the
- * access is skipped and, when `status` is not NULL, the first offending code
- * is recorded in *status (a device int32 the caller zeroes beforehand and may
- * read back whenever it is willing to synchronise).
+ * Device-side index checks: kernels bounds-check every index they read from
+ * device memory before using it: slots and page ids against the pool, table
+ * rows (row_ids / req_ids) against table_rows, lengths against the table's
+ * width.  An out-of-range index is never dereferenced; the access (or the
+ * whole sequence, for a bad row or length) is skipped and, when `status` is
+ * not NULL, the first offending code is recorded in *status (a device int32
+ * the caller zeroes beforehand and may read back whenever it is willing to
+ * synchronise).
  *
  * Stream ordering: kernels are launched with programmatic stream serialisation
  * (programmatic dependent launch).  Each kernel touches q / K / V / the pool /
- * workspaces / outputs only after the previous kernel in the stream has
- * completed, but the split-KV decode kernel plans its work (reads seq_lens,
- * row_ids and the page table) before that point, overlapping the tail of the
- * previous kernel.  Those three metadata arrays must therefore not be produced
- * by the kernel launched IMMEDIATELY before b200kv_paged_decode on the same
- * stream; anything earlier (copies, other kernels) is ordered as usual.
+ * new rows / slot_mapping / workspaces / outputs only after the previous
+ * kernel in the stream has completed, but the decode kernel plans its work
+ * (reads seq_lens, row_ids and the page table) before that point, overlapping
+ * the tail of the previous kernel.  Those three metadata arrays must therefore
+ * not be produced by the kernel launched IMMEDIATELY before a decode entry
+ * point on the same stream -- or that call passes B200KV_DECODE_SERIALIZED,
+ * which launches it as an ordinary, fully ordered kernel.  Anything earlier
+ * (copies, other kernels) is ordered as usual.
  *
  * The reference project (lite_llama, Python + Triton-Ascend) has no native
  * interface; each function below names the reference Python operator whose
@@ -41,7 +46,7 @@
 extern "C" {
 #endif
 
-#define B200KV_VERSION 100
+#define B200KV_VERSION 200
 
 /* ---- host-side return codes ------------------------------------------- */
 #define B200KV_OK              0
@@ -177,46 +182,113 @@ int b200kv_update_kv_index(int32_t* req_to_token_indexs, int64_t row_stride, int
                            int32_t* status, void* stream);
 
 /*
- * Bytes of scratch that b200kv_paged_decode needs for a batch of `batch`
- * sequences on the CURRENT device (split-KV partial outputs and their
- * log-sum-exp).  Depends on the device's SM count.  Returns 0 on bad input.
+ * Bytes of scratch that the decode entry points need for a batch of `batch`
+ * sequences on the CURRENT device: B200KV_DECODE_COUNTER_BYTES of arrival
+ * counters followed by the split-KV partial outputs and their log-sum-exp.
+ * Depends on the device's SM count.  Returns 0 on bad input.
+ *
+ * The counters (one per sequence and KV head, at the start of the workspace
+ * whatever the shape) must be ZERO when a decode call starts.  Every call
+ * leaves them at zero again, so the caller clears the first
+ * B200KV_DECODE_COUNTER_BYTES once, after allocating the workspace
+ * (cudaMemsetAsync), and never again -- unless a call ended with
+ * B200KV_DEV_WAIT_TIMEOUT in *status, after which they must be cleared anew.
+ * Calls that may overlap on the GPU need separate workspaces.
  */
+#define B200KV_DECODE_COUNTER_BYTES (256u << 10)
 size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim);
+
+/* flags of the decode entry points */
+#define B200KV_DECODE_SERIALIZED 1  /* no programmatic overlap with the previous kernel:
+                                       seq_lens / row_ids / table may come straight from it */
 
 /*
  * Paged flash-decoding: one query token per sequence attends to that
  * sequence's whole paged context.  Replaces flash_decoding
  * (lite_llama/kernels/flashdecoding.py:295-342; stage 1 :6-138, stage 2
- * :199-267).  Two launches: a persistent split-KV kernel in which each CTA
- * serves one KV head together with its whole GQA query group, then a
- * log-sum-exp merge of the split partials.
+ * :199-267).  ONE launch: a persistent split-KV kernel in which each CTA
+ * serves one KV head together with its whole GQA query group; the CTA that
+ * delivers the last partial of a sequence merges that sequence's partials
+ * (log-sum-exp weights) and writes its output rows.
  *   q          fp16 [batch, q_heads, head_dim]; strides q_stride_b, q_stride_h
  *   k_base     fp16 K view of the pool, element (t, h, d) at
  *              k_base + t*kv_tok_stride + h*kv_head_stride + d
  *   v_base     likewise for V (same strides)
  *   pool_tokens number of token slots addressable from k_base / v_base
- *   table      int32, row stride table_row_stride, kind B200KV_TABLE_*
+ *   table      int32 [table_rows, table_cols], row stride table_row_stride,
+ *              kind B200KV_TABLE_*
  *   row_ids    int32 [batch] table row of each sequence, or NULL = 0..batch-1
  *              (the reference indexes rows by batch position,
- *              lite_llama/kernels/flashdecoding.py:48,85)
+ *              lite_llama/kernels/flashdecoding.py:48,85); a row outside
+ *              [0, table_rows) sets B200KV_DEV_BAD_LENGTH and that sequence
+ *              is treated as empty
  *   seq_lens   int32 or int64 [batch] (seq_lens_i64 selects); length 0 gives
- *              an all-zero output row
+ *              an all-zero output row; a length above max_seq_len is clamped
+ *              and reported
  *   scale      natural softmax scale (1/sqrt(head_dim)); softmax is base e
- *   max_seq_len host upper bound of the lengths (sizes the launch only)
+ *   max_seq_len host upper bound of the lengths; must fit the table's width
+ *   workspace  see b200kv_decode_workspace_bytes (counters zeroed once)
  *   out        fp16 [batch, q_heads, head_dim]; strides out_stride_b, out_stride_h
- * Supported: head_dim 128, page_size 16, q_heads/kv_heads in [1,16], batch <= 4096.
+ *   flags      0 or B200KV_DECODE_SERIALIZED
+ * Supported: head_dim 128, page_size 16, q_heads/kv_heads in [1,16], batch <= 4096,
+ * batch * kv_heads <= B200KV_DECODE_COUNTER_BYTES / 4.
  */
 int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
                         const void* k_base, const void* v_base,
                         int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
                         const int32_t* table, int64_t table_row_stride, int table_kind,
+                        int table_rows, int64_t table_cols,
                         const int32_t* row_ids,
                         const void* seq_lens, int seq_lens_i64,
                         int batch, int q_heads, int kv_heads, int head_dim, int page_size,
                         float scale, int64_t max_seq_len,
                         void* workspace, size_t workspace_bytes,
                         void* out, int64_t out_stride_b, int64_t out_stride_h,
-                        int32_t* status, void* stream);
+                        int flags, int32_t* status, void* stream);
+
+/*
+ * One decode step of one layer in one launch: the KV append of the step's new
+ * token of every sequence, then paged flash-decoding over the context that
+ * includes it.  Same result as b200kv_kv_append(new_kv, batch, ..., slots, pool)
+ * followed by b200kv_paged_decode(...): update_kv_buffer then flash_decoding in
+ * Attention.token_forward (lite_llama/models/qwen3.py:62-74).  The pool rows
+ * are written bit-exactly.
+ *   new_kv     fp16 [batch, 2*kv_heads, head_dim] (K heads first), token stride
+ *              new_kv_tok_stride: the step's new K/V row of every sequence
+ *   slots      int32 [batch] slot_mapping; slots[b] must be the slot of the LAST
+ *              token of sequence b, i.e. position seq_lens[b] - 1 of its table
+ *              row (seq_lens already counts the new token).  A slot outside the
+ *              pool is skipped, one that is not that position is still written;
+ *              both set B200KV_DEV_BAD_SLOT
+ *   k_base, v_base  as for b200kv_paged_decode, but written to
+ * new_kv and slots may come from the kernel launched immediately before; the
+ * rule for seq_lens / row_ids / table stands.  Sequences of length 0 append
+ * nothing.
+ */
+int b200kv_append_paged_decode(const void* new_kv, int64_t new_kv_tok_stride, const int32_t* slots,
+                               const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                               void* k_base, void* v_base,
+                               int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
+                               const int32_t* table, int64_t table_row_stride, int table_kind,
+                               int table_rows, int64_t table_cols,
+                               const int32_t* row_ids,
+                               const void* seq_lens, int seq_lens_i64,
+                               int batch, int q_heads, int kv_heads, int head_dim, int page_size,
+                               float scale, int64_t max_seq_len,
+                               void* workspace, size_t workspace_bytes,
+                               void* out, int64_t out_stride_b, int64_t out_stride_h,
+                               int flags, int32_t* status, void* stream);
+
+/*
+ * Tuning overrides of the decode launch (no counterpart in the reference); a
+ * value of 0 restores the automatic choice.  Process-wide, not thread-safe
+ * against concurrent decode calls.
+ *   B200KV_OPT_DECODE_TEAMS       upper bound on the teams (CTAs per KV head) of a launch
+ *   B200KV_OPT_DECODE_PIECE_COST  pages of streaming that ending a piece is charged with
+ */
+#define B200KV_OPT_DECODE_TEAMS       1
+#define B200KV_OPT_DECODE_PIECE_COST  2
+int b200kv_set_option(int option, int64_t value);
 
 /*
  * Paged flash-decoding for callers that cannot allocate device memory.
@@ -224,14 +296,15 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * buffers with torch on every call.)
  *
  * Identical to b200kv_paged_decode in arguments, semantics and results, except
- * that there is no workspace argument: the split-KV partials go to a fixed
- * array of B200KV_STATIC_SCRATCH_BYTES that is part of the library image on
- * every GPU that loads it.  Meant for hosts that have no way to get device
- * memory when the call is made -- a server whose device budget was handed to
- * one arena at start-up and which treats any later cudaMalloc as an error, a
- * plug-in whose memory is owned by the embedding application, a real-time loop
- * that cannot risk the device-wide stall an allocation or free can cause.  The
- * call path contains no cudaMalloc / cudaFree and no allocating library call.
+ * that there is no workspace argument: the arrival counters and the split-KV
+ * partials go to a fixed array of B200KV_STATIC_SCRATCH_BYTES that is part of
+ * the library image on every GPU that loads it.  Meant for hosts that have no
+ * way to get device memory when the call is made -- a server whose device
+ * budget was handed to one arena at start-up and which treats any later
+ * cudaMalloc as an error, a plug-in whose memory is owned by the embedding
+ * application, a real-time loop that cannot risk the device-wide stall an
+ * allocation or free can cause.  The call path contains no cudaMalloc /
+ * cudaFree and no allocating library call.
  *
  * Limits and rules:
  *  - the batch must be small enough that b200kv_decode_workspace_bytes() for it
@@ -241,9 +314,10 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  *  - the first call on each device looks up the array's device address (with
  *    that device current) and should be made before any stream capture begins;
  *  - all calls on one device share the one array, which keeps whatever the last
- *    call left there.  Nothing in it needs to start at zero (every partial is
- *    written before it is read), but two calls whose kernels may overlap on the
- *    GPU -- different streams without an ordering between them -- race on it.
+ *    call left there.  The array starts zero-filled and every call returns the
+ *    counters to zero; the partials need no clearing (each is written before it
+ *    is read).  Two calls whose kernels may overlap on the GPU -- different
+ *    streams without an ordering between them -- race on it.
  */
 #define B200KV_STATIC_SCRATCH_BYTES (8u << 20)
 int b200kv_paged_decode_static_scratch(
@@ -251,12 +325,13 @@ int b200kv_paged_decode_static_scratch(
     const void* k_base, const void* v_base,
     int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
     const int32_t* table, int64_t table_row_stride, int table_kind,
+    int table_rows, int64_t table_cols,
     const int32_t* row_ids,
     const void* seq_lens, int seq_lens_i64,
     int batch, int q_heads, int kv_heads, int head_dim, int page_size,
     float scale, int64_t max_seq_len,
     void* out, int64_t out_stride_b, int64_t out_stride_h,
-    int32_t* status, void* stream);
+    int flags, int32_t* status, void* stream);
 
 /*
  * Packed no-pad causal prefill over paged KV with history: query row i of
@@ -267,7 +342,10 @@ int b200kv_paged_decode_static_scratch(
  * (lite_llama/kernels/flashattention2_nopad.py:171-221) once the chunk's own
  * K/V have been appended to the pool.  Tensor-core (tcgen05 / TMEM) kernel.
  *   q          fp16 [total_q, q_heads, head_dim] packed; strides q_stride_t, q_stride_h
- *   req_ids    int32 [batch] table row of each request, or NULL = 0..batch-1
+ *   table      int32 [table_rows, table_cols] (ignored for B200KV_TABLE_DENSE)
+ *   req_ids    int32 [batch] table row of each request, or NULL = 0..batch-1; a
+ *              request whose row is outside the table, or whose ctx + q length
+ *              exceeds the table's width, is skipped (B200KV_DEV_BAD_LENGTH)
  *   q_start    int32 [batch] first packed row of each request
  *   ctx_lens, q_lens  int32 or int64 [batch] (lens_i64 selects)
  *   max_q_len  host upper bound of q_lens (sizes the launch only)
@@ -278,6 +356,7 @@ int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h,
                          const void* k_base, const void* v_base,
                          int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
                          const int32_t* table, int64_t table_row_stride, int table_kind,
+                         int table_rows, int64_t table_cols,
                          const int32_t* req_ids, const int32_t* q_start,
                          const void* ctx_lens, const void* q_lens, int lens_i64,
                          int batch, int64_t total_q, int64_t max_q_len,

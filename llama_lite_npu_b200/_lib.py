@@ -13,7 +13,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200kv.so"
 
-# name -> (restype, argtypes); mirrors include/b200kv.h one to one.
+# name -> (restype, argtypes); mirrors include/b200kv.h and include/b200kv_prefix_cache.h one to one.
 _SIGNATURES = {
     "b200kv_version": (c_int, []),
     "b200kv_strerror": (c_char_p, [c_int]),
@@ -51,37 +51,52 @@ _SIGNATURES = {
          c_void_p, c_void_p],
     ),
     "b200kv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "b200kv_set_option": (c_int, [c_int, c_int64]),
     "b200kv_paged_decode": (
         c_int,
         [c_void_p, c_int64, c_int64,             # q
          c_void_p, c_void_p, c_int64, c_int64, c_int64,   # k, v, strides, pool_tokens
-         c_void_p, c_int64, c_int,               # table
+         c_void_p, c_int64, c_int, c_int, c_int64,        # table, row stride, kind, rows, cols
          c_void_p,                               # row_ids
          c_void_p, c_int,                        # seq_lens
          c_int, c_int, c_int, c_int, c_int,      # batch, heads, dims
          c_float, c_int64,                       # scale, max_seq_len
          c_void_p, c_size_t,                     # workspace
          c_void_p, c_int64, c_int64,             # out
-         c_void_p, c_void_p],                    # status, stream
+         c_int, c_void_p, c_void_p],             # flags, status, stream
+    ),
+    "b200kv_append_paged_decode": (
+        c_int,
+        [c_void_p, c_int64, c_void_p,            # new_kv, token stride, slots
+         c_void_p, c_int64, c_int64,
+         c_void_p, c_void_p, c_int64, c_int64, c_int64,
+         c_void_p, c_int64, c_int, c_int, c_int64,
+         c_void_p,
+         c_void_p, c_int,
+         c_int, c_int, c_int, c_int, c_int,
+         c_float, c_int64,
+         c_void_p, c_size_t,
+         c_void_p, c_int64, c_int64,
+         c_int, c_void_p, c_void_p],
     ),
     "b200kv_paged_decode_static_scratch": (
         c_int,
         [c_void_p, c_int64, c_int64,
          c_void_p, c_void_p, c_int64, c_int64, c_int64,
-         c_void_p, c_int64, c_int,
+         c_void_p, c_int64, c_int, c_int, c_int64,
          c_void_p,
          c_void_p, c_int,
          c_int, c_int, c_int, c_int, c_int,
          c_float, c_int64,
          c_void_p, c_int64, c_int64,
-         c_void_p, c_void_p],
+         c_int, c_void_p, c_void_p],
     ),
     "b200kv_selftest_bounded_wait": (c_int, [c_uint64, c_void_p, c_void_p, c_void_p]),
     "b200kv_paged_prefill": (
         c_int,
         [c_void_p, c_int64, c_int64,
          c_void_p, c_void_p, c_int64, c_int64, c_int64,
-         c_void_p, c_int64, c_int,
+         c_void_p, c_int64, c_int, c_int, c_int64,
          c_void_p, c_void_p,
          c_void_p, c_void_p, c_int,
          c_int, c_int64, c_int64,
@@ -90,6 +105,16 @@ _SIGNATURES = {
          c_void_p, c_int64, c_int64,
          c_void_p, c_void_p],
     ),
+    # host-side prefix cache (include/b200kv_prefix_cache.h)
+    "b200kv_prefix_cache_create": (c_void_p, [c_int, c_int64, c_int64]),
+    "b200kv_prefix_cache_destroy": (None, [c_void_p]),
+    "b200kv_prefix_cache_entries": (c_int64, [c_void_p, c_int]),
+    "b200kv_prefix_cache_lookup_exact": (
+        c_int64, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
+    "b200kv_prefix_cache_lookup_blocks": (c_int64, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "b200kv_prefix_cache_store": (c_int64, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
+    "b200kv_prefix_cache_ref_ops": (c_int64, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "b200kv_prefix_cache_clear": (c_int64, [c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

@@ -28,6 +28,7 @@ SOURCES = (
     "paged_decode.cu",
     "tma.cu",
     "paged_prefill_sm100.cu",
+    "prefix_cache.cpp",
 )
 
 NVCC_FLAGS = (
@@ -48,7 +49,8 @@ def _find_nvcc() -> str:
 
 def _source_digest() -> str:
     h = hashlib.sha256()
-    files = sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    files = (sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+             + sorted(CSRC.glob("*.cpp")))
     files += sorted(INCLUDE.glob("*.h"))
     for f in files:
         h.update(f.name.encode())

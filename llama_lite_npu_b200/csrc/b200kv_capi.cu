@@ -152,14 +152,14 @@ size_t b200kv_decode_workspace_bytes(int batch, int q_heads, int kv_heads, int h
   return b200kv::decode_workspace_bytes(batch, q_heads, kv_heads, head_dim);
 }
 
-int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_base,
-                        const void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
-                        int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
-                        int table_kind, const int32_t* row_ids, const void* seq_lens,
-                        int seq_lens_i64, int batch, int q_heads, int kv_heads, int head_dim,
-                        int page_size, float scale, int64_t max_seq_len, void* workspace,
-                        size_t workspace_bytes, void* out, int64_t out_stride_b,
-                        int64_t out_stride_h, int32_t* status, void* stream) {
+namespace {
+b200kv::DecodeArgs decode_args(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_base,
+                               const void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
+                               int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
+                               int table_kind, int table_rows, int64_t table_cols, const int32_t* row_ids,
+                               const void* seq_lens, int seq_lens_i64, int batch, int q_heads, int kv_heads,
+                               int head_dim, int page_size, float scale, int64_t max_seq_len, void* out,
+                               int64_t out_stride_b, int64_t out_stride_h, int flags, int32_t* status) {
   b200kv::DecodeArgs a{};
   a.q = q;
   a.q_stride_b = q_stride_b;
@@ -172,6 +172,8 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, c
   a.table = table;
   a.table_row_stride = table_row_stride;
   a.table_kind = table_kind;
+  a.table_rows = table_rows;
+  a.table_cols = table_cols;
   a.row_ids = row_ids;
   a.seq_lens = seq_lens;
   a.seq_lens_i64 = seq_lens_i64;
@@ -182,57 +184,79 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, c
   a.page_size = page_size;
   a.scale = scale;
   a.max_seq_len = max_seq_len;
-  a.workspace = workspace;
-  a.workspace_bytes = workspace_bytes;
   a.out = out;
   a.out_stride_b = out_stride_b;
   a.out_stride_h = out_stride_h;
+  a.flags = flags;
   a.status = status;
+  return a;
+}
+}  // namespace
+
+int b200kv_set_option(int option, int64_t value) { return b200kv::set_decode_option(option, value); }
+
+int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_base,
+                        const void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
+                        int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
+                        int table_kind, int table_rows, int64_t table_cols, const int32_t* row_ids,
+                        const void* seq_lens, int seq_lens_i64, int batch, int q_heads, int kv_heads,
+                        int head_dim, int page_size, float scale, int64_t max_seq_len, void* workspace,
+                        size_t workspace_bytes, void* out, int64_t out_stride_b, int64_t out_stride_h,
+                        int flags, int32_t* status, void* stream) {
+  b200kv::DecodeArgs a = decode_args(q, q_stride_b, q_stride_h, k_base, v_base, kv_tok_stride, kv_head_stride,
+                                     pool_tokens, table, table_row_stride, table_kind, table_rows, table_cols,
+                                     row_ids, seq_lens, seq_lens_i64, batch, q_heads, kv_heads, head_dim,
+                                     page_size, scale, max_seq_len, out, out_stride_b, out_stride_h, flags,
+                                     status);
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
+  return b200kv::paged_decode(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200kv_append_paged_decode(const void* new_kv, int64_t new_kv_tok_stride, const int32_t* slots,
+                               const void* q, int64_t q_stride_b, int64_t q_stride_h, void* k_base,
+                               void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
+                               int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
+                               int table_kind, int table_rows, int64_t table_cols, const int32_t* row_ids,
+                               const void* seq_lens, int seq_lens_i64, int batch, int q_heads,
+                               int kv_heads, int head_dim, int page_size, float scale,
+                               int64_t max_seq_len, void* workspace, size_t workspace_bytes, void* out,
+                               int64_t out_stride_b, int64_t out_stride_h, int flags, int32_t* status,
+                               void* stream) {
+  if (batch > 0 && (new_kv == nullptr || slots == nullptr)) return B200KV_EINVAL;
+  b200kv::DecodeArgs a = decode_args(q, q_stride_b, q_stride_h, k_base, v_base, kv_tok_stride, kv_head_stride,
+                                     pool_tokens, table, table_row_stride, table_kind, table_rows, table_cols,
+                                     row_ids, seq_lens, seq_lens_i64, batch, q_heads, kv_heads, head_dim,
+                                     page_size, scale, max_seq_len, out, out_stride_b, out_stride_h, flags,
+                                     status);
+  a.new_kv = new_kv;
+  a.new_kv_tok_stride = new_kv_tok_stride;
+  a.slots = slots;
+  a.workspace = workspace;
+  a.workspace_bytes = workspace_bytes;
   return b200kv::paged_decode(a, static_cast<cudaStream_t>(stream));
 }
 
 int b200kv_paged_decode_static_scratch(
     const void* q, int64_t q_stride_b, int64_t q_stride_h, const void* k_base, const void* v_base,
     int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens, const int32_t* table,
-    int64_t table_row_stride, int table_kind, const int32_t* row_ids, const void* seq_lens,
-    int seq_lens_i64, int batch, int q_heads, int kv_heads, int head_dim, int page_size, float scale,
-    int64_t max_seq_len, void* out, int64_t out_stride_b, int64_t out_stride_h, int32_t* status,
-    void* stream) {
-  b200kv::DecodeArgs a{};
-  a.q = q;
-  a.q_stride_b = q_stride_b;
-  a.q_stride_h = q_stride_h;
-  a.k_base = k_base;
-  a.v_base = v_base;
-  a.kv_tok_stride = kv_tok_stride;
-  a.kv_head_stride = kv_head_stride;
-  a.pool_tokens = pool_tokens;
-  a.table = table;
-  a.table_row_stride = table_row_stride;
-  a.table_kind = table_kind;
-  a.row_ids = row_ids;
-  a.seq_lens = seq_lens;
-  a.seq_lens_i64 = seq_lens_i64;
-  a.batch = batch;
-  a.q_heads = q_heads;
-  a.kv_heads = kv_heads;
-  a.head_dim = head_dim;
-  a.page_size = page_size;
-  a.scale = scale;
-  a.max_seq_len = max_seq_len;
-  a.workspace = nullptr;
-  a.workspace_bytes = 0;
-  a.out = out;
-  a.out_stride_b = out_stride_b;
-  a.out_stride_h = out_stride_h;
-  a.status = status;
+    int64_t table_row_stride, int table_kind, int table_rows, int64_t table_cols, const int32_t* row_ids,
+    const void* seq_lens, int seq_lens_i64, int batch, int q_heads, int kv_heads, int head_dim,
+    int page_size, float scale, int64_t max_seq_len, void* out, int64_t out_stride_b,
+    int64_t out_stride_h, int flags, int32_t* status, void* stream) {
+  b200kv::DecodeArgs a = decode_args(q, q_stride_b, q_stride_h, k_base, v_base, kv_tok_stride, kv_head_stride,
+                                     pool_tokens, table, table_row_stride, table_kind, table_rows, table_cols,
+                                     row_ids, seq_lens, seq_lens_i64, batch, q_heads, kv_heads, head_dim,
+                                     page_size, scale, max_seq_len, out, out_stride_b, out_stride_h, flags,
+                                     status);
   return b200kv::paged_decode_static_scratch(a, static_cast<cudaStream_t>(stream));
 }
 
 int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h, const void* k_base,
                          const void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
                          int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
-                         int table_kind, const int32_t* req_ids, const int32_t* q_start,
+                         int table_kind, int table_rows, int64_t table_cols, const int32_t* req_ids,
+                         const int32_t* q_start,
                          const void* ctx_lens, const void* q_lens, int lens_i64, int batch,
                          int64_t total_q, int64_t max_q_len, int q_heads, int kv_heads, int head_dim,
                          int page_size, float scale_log2, void* out, int64_t out_stride_t,
@@ -249,6 +273,8 @@ int b200kv_paged_prefill(const void* q, int64_t q_stride_t, int64_t q_stride_h, 
   a.table = table;
   a.table_row_stride = table_row_stride;
   a.table_kind = table_kind;
+  a.table_rows = table_rows;
+  a.table_cols = table_cols;
   a.req_ids = req_ids;
   a.q_start = q_start;
   a.ctx_lens = ctx_lens;

@@ -41,19 +41,24 @@ __global__ void __launch_bounds__(128) decode_advance_kernel(AdvanceParams p) {
   if (b >= p.batch) return;
   const int row = p.req_ids ? p.req_ids[b] : b;
   const int64_t pos = load_len(p.seq_lens, p.seq_lens_i64, b);   // index of the new token
+  // A refused sequence gets slot -1 (the append and the prologue skip negative slots); left alone,
+  // slots[b] would still name the previous step's row and the next append would overwrite it.
   if (row < 0 || row >= p.table_rows || pos < 0) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
+    p.slots[b] = -1;
     return;
   }
   const int64_t page_idx = pos / p.page_size;
   if (page_idx >= p.table_pages || (p.page_counts && page_idx >= p.page_counts[row]) ||
       (p.token_table && pos >= p.token_cols)) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);   // no page reserved for the new token
+    p.slots[b] = -1;
     return;
   }
   const int64_t page = p.block_table[row * p.block_row_stride + page_idx];
   if (page < 0 || page >= p.pool_pages) {
     set_status(p.status, B200KV_DEV_BAD_PAGE);
+    p.slots[b] = -1;
     return;
   }
   const int32_t slot = static_cast<int32_t>(page * p.page_size + (pos - page_idx * p.page_size));

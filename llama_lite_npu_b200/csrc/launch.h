@@ -72,9 +72,14 @@ struct DecodeArgs {
   const int32_t* table;
   int64_t table_row_stride;
   int table_kind;
+  int table_rows;
+  int64_t table_cols;
   const int32_t* row_ids;
   const void* seq_lens;
   int seq_lens_i64;
+  const void* new_kv;          // fused append: nullptr = none
+  int64_t new_kv_tok_stride;
+  const int32_t* slots;
   int batch, q_heads, kv_heads, head_dim, page_size;
   float scale;
   int64_t max_seq_len;
@@ -82,9 +87,11 @@ struct DecodeArgs {
   size_t workspace_bytes;
   void* out;
   int64_t out_stride_b, out_stride_h;
+  int flags;
   int32_t* status;
 };
 size_t decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim);
+int set_decode_option(int option, int64_t value);
 int paged_decode(const DecodeArgs& a, cudaStream_t stream);
 // Same, with the split-KV scratch in a fixed device array owned by the library (args.workspace ignored).
 int paged_decode_static_scratch(const DecodeArgs& args, cudaStream_t stream);
@@ -98,6 +105,8 @@ struct PrefillArgs {
   const int32_t* table;
   int64_t table_row_stride;
   int table_kind;
+  int table_rows;
+  int64_t table_cols;
   const int32_t* req_ids;
   const int32_t* q_start;
   const void* ctx_lens;

@@ -1,4 +1,5 @@
-// Paged flash-decoding for B200: persistent split-KV kernel + log-sum-exp merge.
+// Paged flash-decoding for B200: one persistent split-KV launch that also merges its partials
+// and, when asked, performs the step's KV append.
 //
 // Replaces flash_decoding of the reference (lite_llama/kernels/flashdecoding.py:295-342):
 // stage 1 there launches one program per (sequence, QUERY head, 128-token partition), so
@@ -13,13 +14,20 @@
 //     [i*U/nteams, (i+1)*U/nteams) of that line and CTA k of the team handles KV head k over
 //     it, so every CTA has the same work whatever the length mix, and the Hkv CTAs of a team
 //     sweep the same token rows (one 2*Hkv*128-half pool row holds all heads of a token) at
-//     the same time.  The line is measured in units, U = NP + kPieceCost per non-empty
+//     the same time.  The line is measured in units, U = NP + piece_cost per non-empty
 //     sequence: ending a piece costs a CTA about that many pages of streaming, and a cut
 //     inside a sequence's extra units snaps to the start of the sequence;
 //   * a team's range may cover the tail of one sequence, several whole sequences and the
 //     head of another: each such "piece" yields either the final fp16 output (piece ==
 //     whole sequence) or an fp32 partial (normalised output + log2-domain log-sum-exp) in
-//     slot team + b of the workspace, merged afterwards by decode_combine_kernel.
+//     slot team + b of the workspace.  The CTA that delivers the LAST partial of a (sequence,
+//     KV head) -- found with a wrapping atomic counter that is back at zero when the launch
+//     ends -- merges all of them (stage 2 of the reference, flashdecoding.py:199-267) and
+//     writes the fp16 rows, so the whole decode is ONE launch;
+//   * optionally the step's KV append is part of the same launch: the CTA whose range holds
+//     the last page of a sequence writes that sequence's new K and V row of its head into the
+//     pool (update_kv_buffer of the reference, update_kv_buffer.py:47-81) right before it
+//     fetches that page.
 //
 // Pipeline inside a CTA (5 warps, 2 CTAs per SM): tiles of 64 tokens (4 pages; K and V rows
 // of 256 B each) flow through a 3-deep ring of 32 KB stages that keeps running across piece
@@ -30,9 +38,11 @@
 // (tokens [16w, 16w+16)) of every tile: S^T = K Q^T and O^T += V^T P^T run on mma.sync
 // m16n8k16 (fp16 in, fp32 accumulate) with the tokens as the M rows and the G query heads as
 // the N columns; per-warp online-softmax states are merged through shared memory at the end
-// of a piece (two named barriers among the four consumer warps; the next sequence's Q is
+// of a piece (named barriers among the four consumer warps; the next sequence's Q is
 // requested before the merge so that its latency hides under it).  No CTA-wide barrier in the
-// steady state; every mbarrier wait is time-bounded.
+// steady state; every mbarrier wait is time-bounded, and a consumer warp whose wait ran out
+// keeps walking its tiles without computing, so it still meets the other warps at every named
+// barrier and the arrival counters end at zero.
 // The kernel is HBM-bound: algorithmic bytes per token per KV head = 2 (K,V) * 128 * 2 B.
 #include "common.cuh"
 #include "launch.h"
@@ -47,48 +57,37 @@ constexpr int kPS = 16;
 constexpr int kTileTok = 64;
 constexpr int kTilePages = kTileTok / kPS;
 constexpr int kConsumerWarps = 4;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;  // + one producer warp
 constexpr int kScanThreads = 128;
 constexpr int kRowBytes = kD * 2;
 constexpr int kPageBytes = kPS * kRowBytes;       // one page of one head, K or V: 4 KB
 constexpr int kTileBytes = kTileTok * kRowBytes;  // one of K or V
 constexpr int kStageBytes = 2 * kTileBytes;
-// Tunables; the -D overrides exist for tuning sweeps, the defaults are what ships.
-#ifndef B200KV_DECODE_CTAS_PER_SM
-#define B200KV_DECODE_CTAS_PER_SM 2
-#endif
-#ifndef B200KV_DECODE_STAGES
-#define B200KV_DECODE_STAGES 3
-#endif
-constexpr int kCtasPerSm = B200KV_DECODE_CTAS_PER_SM;
-constexpr int kStagesRows8 = B200KV_DECODE_STAGES;
-#ifndef B200KV_DECODE_L2_PREFETCH
-#define B200KV_DECODE_L2_PREFETCH 2   // tiles prefetched into L2 before the dependency wait (<= kLead)
-#endif
-#ifndef B200KV_DECODE_MIN_PAGES
-#define B200KV_DECODE_MIN_PAGES 4
-#endif
-constexpr int kMinPagesPerTeam = B200KV_DECODE_MIN_PAGES;   // a team is not worth launching for fewer pages
+constexpr int kCtasPerSm = 2;
+constexpr int kStagesRows8 = 3;
+constexpr int kL2PrefetchTiles = 2;   // tiles prefetched into L2 before the dependency wait (<= kLead)
+constexpr int kMinPagesPerTeam = 4;   // a team is not worth launching for fewer pages
 // Ending a piece (merging the four warps' state, writing the rows, restarting on another
 // sequence) costs a CTA about as much as streaming this many pages.  The page line is therefore
 // split in UNITS: every non-empty sequence counts its pages plus this constant, so that teams
 // with more sequence boundaries get fewer pages; a team boundary that falls inside a sequence's
 // extra units snaps to the start of that sequence.
-#ifndef B200KV_DECODE_PIECE_COST
-#define B200KV_DECODE_PIECE_COST 8
-#endif
-constexpr int kPieceCost = B200KV_DECODE_PIECE_COST;
-constexpr int kCombineThreads = 256;   // at most; the launch picks 128 or 256
+constexpr int kDefaultPieceCost = 8;
+// The first bytes of the workspace hold one arrival counter per (sequence, KV head).
+constexpr size_t kCounterBytes = B200KV_DECODE_COUNTER_BYTES;
+constexpr int64_t kMaxCounters = static_cast<int64_t>(kCounterBytes / sizeof(unsigned));
 
 struct DecodeParams {
   const __half* q;
   int64_t q_stride_b, q_stride_h;
-  const __half* k_base;
-  const __half* v_base;
+  __half* k_base;
+  __half* v_base;
   int64_t kv_tok_stride, kv_head_stride, pool_tokens;
   const int32_t* table;
   int64_t table_row_stride;
   int table_kind;
+  int table_rows;
   const int32_t* row_ids;
   const void* seq_lens;
   int seq_lens_i64;
@@ -96,13 +95,22 @@ struct DecodeParams {
   float scale_log2;
   int64_t max_seq_len;
   int nteams;
-  float* part_o;    // [nslots][kv_heads][ROWS][128]
-  float* part_lse;  // [nslots][kv_heads][ROWS]
+  int piece_cost;
+  // fused KV append (new_kv == nullptr: none): pool[slots[b]] = new_kv[b] for this CTA's head
+  const __half* new_kv;       // [batch][2*kv_heads][128], K heads first
+  int64_t new_kv_tok_stride;
+  const int32_t* slots;
+  float* part_o;        // [nslots][kv_heads][ROWS][128]
+  float* part_lse;      // [nslots][kv_heads][ROWS]
+  unsigned* piece_ctr;  // [batch][kv_heads], zero between launches
   __half* out;
   int64_t out_stride_b, out_stride_h;
   int32_t* status;
 };
 
+// Length of sequence b as every part of the kernel sees it: clamped to [0, max_seq_len] (the
+// host made sure max_seq_len fits the table's width), and 0 when its table row does not exist,
+// so a stale length or request id can never turn into a read outside the table.
 __device__ __forceinline__ int seq_len_checked(const DecodeParams& p, int b) {
   int64_t len = load_len(p.seq_lens, p.seq_lens_i64, b);
   if (len < 0) {
@@ -111,6 +119,13 @@ __device__ __forceinline__ int seq_len_checked(const DecodeParams& p, int b) {
   } else if (len > p.max_seq_len) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
     len = p.max_seq_len;
+  }
+  if (p.row_ids != nullptr) {
+    const int row = __ldg(p.row_ids + b);
+    if (row < 0 || row >= p.table_rows) {
+      set_status(p.status, B200KV_DEV_BAD_LENGTH);
+      len = 0;
+    }
   }
   return static_cast<int>(len);
 }
@@ -123,12 +138,12 @@ __device__ __forceinline__ int effective_teams(int nteams, int64_t np_total) {
   if (t < 1) t = 1;
   return static_cast<int>(t);
 }
-__device__ __forceinline__ int64_t team_begin(int team, int nteams_eff, int64_t np_total) {
-  return (static_cast<int64_t>(team) * np_total) / nteams_eff;
+__device__ __forceinline__ int64_t team_begin(int team, int nteams_eff, int64_t total) {
+  return (static_cast<int64_t>(team) * total) / nteams_eff;
 }
-// Team whose range holds flat page x (0 <= x < np_total).
-__device__ __forceinline__ int team_of(int64_t x, int nteams_eff, int64_t np_total) {
-  return static_cast<int>(((x + 1) * nteams_eff - 1) / np_total);
+// Team whose range holds position x (0 <= x < total).
+__device__ __forceinline__ int team_of(int64_t x, int nteams_eff, int64_t total) {
+  return static_cast<int>(((x + 1) * nteams_eff - 1) / total);
 }
 
 struct Tile {
@@ -137,6 +152,9 @@ struct Tile {
   int page0;    // first logical page of the tile
   int npages;   // pages in the tile (1..4)
   int ntok;     // valid tokens in the tile
+  int np;       // pages of the whole sequence
+  int len;      // tokens of the whole sequence
+  int64_t units0;  // unit position of the sequence's start on the line
   bool first;   // first tile of its piece
   bool last;    // last tile of its piece
   bool whole;   // the piece is the whole sequence
@@ -148,6 +166,7 @@ struct Walker {
   int b;
   int64_t flat, flat_end;
   int page, piece_begin, piece_end, np, len, row;
+  int kseq;   // non-empty sequences before b
 
   __device__ __forceinline__ void enter(const DecodeParams& p, int seq, int first_page) {
     b = seq;
@@ -167,6 +186,7 @@ struct Walker {
         flat = flat_end;
         return false;
       }
+      ++kseq;
       enter(p, nb, 0);
     }
     t.b = b;
@@ -175,6 +195,9 @@ struct Walker {
     t.npages = min(kTilePages, piece_end - page);
     const int tok_end = min(len, (page + t.npages) * kPS);
     t.ntok = tok_end - page * kPS;
+    t.np = np;
+    t.len = len;
+    t.units0 = (flat - page) + static_cast<int64_t>(p.piece_cost) * kseq;
     t.first = (page == piece_begin);
     t.last = (page + t.npages == piece_end);
     t.whole = (piece_begin == 0 && piece_end == np);
@@ -187,17 +210,42 @@ struct Walker {
 // What the producer needs to issue one tile.  The table entries are kept RAW (undecoded and
 // unchecked) so that nothing depends on the loaded values until the tile is issued, kLead
 // tiles after the loads were started: the table latency is off the producer's critical path.
+// A tile that holds the last page of its sequence also carries this lane's 16 bytes of the
+// sequence's new K (lanes 0..15) or V (lanes 16..31) row when the append is fused.
 constexpr int kLead = 4;
 struct Fetch {
   int ntok;    // valid tokens of the tile; 0 = no tile
   int npages;  // pages of the tile
   int32_t id[kTilePages];
+  int app_b;         // >= 0: the tile ends this sequence, whose new row is written before the tile is fetched
+  int app_off;       // offset of that row inside the sequence's last page
+  int32_t app_slot;  // slot_mapping entry of that row
+  uint32_t app_row0, app_row1, app_row2, app_row3;   // this lane's 16 bytes of the row
 };
 
-__device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fetch& f) {
+// This lane's 16 bytes of the new row of sequence f.app_b, and the slot it goes to.  The new rows
+// and the slot_mapping usually come from the kernel launched just before this one, so they are
+// only read after the dependency wait.
+__device__ __forceinline__ void load_new_row(const DecodeParams& p, Fetch& f, int head, int lane) {
+  f.app_slot = __ldg(p.slots + f.app_b);
+  const __half* src = p.new_kv + static_cast<int64_t>(f.app_b) * p.new_kv_tok_stride +
+                      static_cast<int64_t>((lane < 16 ? 0 : p.kv_heads) + head) * kD + (lane & 15) * 8;
+  const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));
+  f.app_row0 = v.x;
+  f.app_row1 = v.y;
+  f.app_row2 = v.z;
+  f.app_row3 = v.w;
+}
+
+__device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fetch& f, int head, int lane,
+                                           bool after_wait) {
   Tile t;
   f.ntok = 0;
   f.npages = 0;
+  f.app_b = -1;
+  f.app_off = 0;
+  f.app_slot = -1;
+  f.app_row0 = f.app_row1 = f.app_row2 = f.app_row3 = 0u;
 #pragma unroll
   for (int i = 0; i < kTilePages; ++i) f.id[i] = 0;
   if (!w.next(p, t)) return;
@@ -211,14 +259,19 @@ __device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fet
       f.id[i] = __ldg(rowp + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
     }
   }
+  if (p.new_kv != nullptr && t.page0 + t.npages == t.np) {
+    f.app_b = t.b;
+    f.app_off = (t.len - 1) & (kPS - 1);
+    if (after_wait) load_new_row(p, f, head, lane);
+  }
 }
 
 // Programmatic dependent launch, used by every kernel of this library the same way: whatever
 // a kernel does BEFORE this call may overlap the tail of the previous kernel in the stream, so
 // it must only read launch metadata (lengths, row ids, page table) that an earlier, already
-// completed operation produced.  Releasing our own dependents only after our own wait keeps the
-// guarantee transitive: when a dependent's prologue runs, everything two or more kernels back
-// has completed.
+// completed operation produced.  Every thread of every CTA makes this call on every path, early
+// exits included, and a kernel releases its own dependents only after its own wait: when a
+// dependent's prologue runs, everything two or more kernels back has completed.
 __device__ __forceinline__ void pdl_wait_then_trigger() {
   cudaGridDependencySynchronize();
   cudaTriggerProgrammaticLaunchCompletion();
@@ -238,6 +291,70 @@ __device__ __forceinline__ uint32_t page_chunk_off(int r, int c) {
   return static_cast<uint32_t>(((c >> 3) << 11) + (r << 7) + (((c & 7) ^ (r & 7)) << 4));
 }
 
+__device__ __forceinline__ void consumer_bar() {
+  asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerThreads) : "memory");
+}
+
+// Merge the `npieces` partials of (sequence b, KV head `head`) held in slots t_first + b ...:
+// out = sum_p 2^(lse_p - M) o_p / sum_p 2^(lse_p - M).  Run by the 128 consumer threads of the CTA
+// that delivered the last partial; thread = output column, rows eight at a time, the loads of
+// kMergeBatch pieces in flight together.  The partials were written by other CTAs: read them past L1.
+constexpr int kMergeBatch = 2;
+template <int ROWS>
+__device__ __forceinline__ void merge_pieces(const DecodeParams& p, int b, int head, int t_first,
+                                             int npieces, int tid) {
+#pragma unroll 1
+  for (int r0 = 0; r0 < ROWS && r0 < p.group; r0 += 8) {
+    float M[8], L[8], acc[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      M[r] = -INFINITY;
+      L[r] = acc[r] = 0.f;
+    }
+#pragma unroll 1
+    for (int pc = 0; pc < npieces; ++pc) {
+      const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head;
+      const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0));
+      const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0 + 4));
+      M[0] = fmaxf(M[0], a.x); M[1] = fmaxf(M[1], a.y); M[2] = fmaxf(M[2], a.z); M[3] = fmaxf(M[3], a.w);
+      M[4] = fmaxf(M[4], c.x); M[5] = fmaxf(M[5], c.y); M[6] = fmaxf(M[6], c.z); M[7] = fmaxf(M[7], c.w);
+    }
+#pragma unroll 1
+    for (int p0 = 0; p0 < npieces; p0 += kMergeBatch) {
+      float lse[kMergeBatch][8], ov[kMergeBatch][8];
+#pragma unroll
+      for (int j = 0; j < kMergeBatch; ++j) {
+        const int pc = min(p0 + j, npieces - 1);
+        const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head;
+        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0));
+        const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0 + 4));
+        lse[j][0] = a.x; lse[j][1] = a.y; lse[j][2] = a.z; lse[j][3] = a.w;
+        lse[j][4] = c.x; lse[j][5] = c.y; lse[j][6] = c.z; lse[j][7] = c.w;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
+      }
+#pragma unroll
+      for (int j = 0; j < kMergeBatch; ++j) {
+        if (p0 + j < npieces) {
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float w = fast_exp2(lse[j][r] - M[r]);
+            L[r] += w;
+            acc[r] += w * ov[j][r];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+      if (r0 + r < p.group)
+        p.out[static_cast<int64_t>(b) * p.out_stride_b +
+              (static_cast<int64_t>(head) * p.group + r0 + r) * p.out_stride_h + tid] =
+            __float2half_rn(acc[r] / L[r]);
+    }
+  }
+}
+
 // Kernel structure: warp 4 is the producer (walks the page line, waits for a free stage, arms
 // its "full" mbarrier with the byte count and issues the tile's 16 TMA copies from 16 lanes);
 // warps 0..3 are consumers (wait "full", compute their page of the tile, arrive on "empty").
@@ -250,8 +367,8 @@ __device__ __forceinline__ uint32_t page_chunk_off(int r, int c) {
 // uses two N blocks.
 template <int ROWS, int STAGES>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
-                          const __grid_constant__ CUtensorMap vmap) {
+paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap) {
   static_assert(ROWS == 8 || ROWS == 16, "query-group heads are padded to 8 or 16");
   constexpr int NB = ROWS / 8;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -259,6 +376,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   float* merge_o = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [4][128][ROWS]
   float* merge_ml = merge_o + kConsumerWarps * kD * ROWS;                  // [4][ROWS][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(merge_ml + kConsumerWarps * ROWS * 2);
+  int* verdict = reinterpret_cast<int*>(bars + 2 * STAGES);  // [2]: pieces to merge (0 = not last), first team
   int* scan = reinterpret_cast<int*>(merge_o);  // start-up only: [kScanThreads + 1] page prefix
 
   const int tid = threadIdx.x;
@@ -271,6 +389,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const uint32_t bar_empty = bar_full + 8 * STAGES;         // [STAGES]
   if ((stage_base & 1023u) != 0) {  // the swizzled TMA boxes need 1024-byte aligned stages
     set_status(p.status, B200KV_DEV_BAD_PAGE);
+    pdl_wait_then_trigger();
     return;
   }
   if (tid == 0) {
@@ -283,7 +402,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   }
 
   // ---- where does this team's range start and end? -----------------------------------------
-  // Thread t < 128 sums the units (pages + kPieceCost per non-empty sequence) and the non-empty
+  // Thread t < 128 sums the units (pages + piece_cost per non-empty sequence) and the non-empty
   // sequences of [t*per, (t+1)*per); scans over the 128 sums give the totals and the chunk holding
   // a boundary, then a short linear walk finds the sequence.
   int* scan_k = scan + kScanThreads + 1;   // non-empty sequences, same indexing
@@ -294,7 +413,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     const int hi = min(p.batch, lo + per);
     for (int b = lo; b < hi; ++b) {
       const int np = pages_of(seq_len_checked(p, b));
-      sum += np + (np > 0 ? kPieceCost : 0);
+      sum += np + (np > 0 ? p.piece_cost : 0);
       cnt += np > 0;
     }
     scan[tid + 1] = sum;
@@ -323,52 +442,57 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   }
   __syncthreads();
   const int64_t units_total = scan[kScanThreads];
-  const int64_t np_total = units_total - static_cast<int64_t>(kPieceCost) * scan_k[kScanThreads];
+  const int nonempty_total = scan_k[kScanThreads];
+  const int64_t np_total = units_total - static_cast<int64_t>(p.piece_cost) * nonempty_total;
   const int nteams_eff = effective_teams(p.nteams, np_total);
-  if (np_total == 0 || team >= nteams_eff) return;
+  const bool any_empty = nonempty_total < p.batch;
 
   // Unit position x -> (sequence, page inside it, flat page index).  Positions inside a sequence's
-  // kPieceCost extra units map to its first page.
-  int start_b = 0, start_page = 0;
+  // piece_cost extra units map to its first page.
+  int start_b = 0, start_page = 0, start_k = 0;
   int64_t r_begin = 0, r_end = 0;
+  if (np_total > 0 && team < nteams_eff) {
 #pragma unroll 1
-  for (int side = 0; side < 2; ++side) {
-    const int64_t x = team_begin(team + side, nteams_eff, units_total);
-    int64_t flat;
-    int sb = 0, sp = 0;
-    if (x >= units_total) {
-      flat = np_total;
-    } else {
-      int lo = 0, hi = kScanThreads - 1;   // last chunk whose unit prefix <= x
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (scan[mid] <= x) lo = mid; else hi = mid - 1;
+    for (int side = 0; side < 2; ++side) {
+      const int64_t x = team_begin(team + side, nteams_eff, units_total);
+      int64_t flat = np_total;
+      int sb = 0, sp = 0, sk = 0;
+      if (x < units_total) {
+        int lo = 0, hi = kScanThreads - 1;   // last chunk whose unit prefix <= x
+        while (lo < hi) {
+          const int mid = (lo + hi + 1) >> 1;
+          if (scan[mid] <= x) lo = mid; else hi = mid - 1;
+        }
+        int64_t acc = scan[lo];
+        sk = scan_k[lo];
+        int64_t pages_before = acc - static_cast<int64_t>(p.piece_cost) * sk;
+        int b = lo * per;
+        for (; b < p.batch; ++b) {   // ends before the batch does when the lengths are consistent
+          const int np = pages_of(seq_len_checked(p, b));
+          const int w = np + (np > 0 ? p.piece_cost : 0);
+          if (acc + w > x) break;
+          acc += w;
+          pages_before += np;
+          sk += np > 0;
+        }
+        if (b < p.batch) {
+          const int64_t o = x - acc - p.piece_cost;
+          sb = b;
+          sp = o > 0 ? static_cast<int>(o) : 0;
+          flat = pages_before + sp;
+        }
       }
-      int64_t acc = scan[lo];
-      int64_t pages_before = acc - static_cast<int64_t>(kPieceCost) * scan_k[lo];
-      int b = lo * per;
-      for (;;) {
-        const int np = pages_of(seq_len_checked(p, b));
-        const int w = np + (np > 0 ? kPieceCost : 0);
-        if (acc + w > x) break;
-        acc += w;
-        pages_before += np;
-        ++b;
+      if (side == 0) {
+        start_b = sb;
+        start_page = sp;
+        start_k = sk;
+        r_begin = flat;
+      } else {
+        r_end = flat;
       }
-      const int64_t o = x - acc - kPieceCost;
-      sb = b;
-      sp = o > 0 ? static_cast<int>(o) : 0;
-      flat = pages_before + sp;
-    }
-    if (side == 0) {
-      start_b = sb;
-      start_page = sp;
-      r_begin = flat;
-    } else {
-      r_end = flat;
     }
   }
-  if (r_end <= r_begin) return;   // a range that lay wholly inside a sequence's extra units
+  const bool has_range = r_end > r_begin;   // false also for a range wholly inside a sequence's extra units
   __syncthreads();  // the scan scratch aliases the merge buffer; barrier inits are visible
 
   // ================================= producer warp ==========================================
@@ -376,6 +500,10 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   // "full" barrier with the byte count, then lanes 0..15 each issue ONE of the tile's copies:
   // lane = 4*page + {K low half, K high half, V low half, V high half}.
   if (warp == kConsumerWarps) {
+    if (!has_range) {
+      pdl_wait_then_trigger();
+      return;
+    }
     if (lane == 0) {
       prefetch_tensormap(&kmap);
       prefetch_tensormap(&vmap);
@@ -384,18 +512,18 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     Walker prod;
     prod.flat = r_begin;
     prod.flat_end = r_end;
+    prod.kseq = start_k;
     prod.enter(p, start_b, start_page);
     Fetch fq[kLead];
 #pragma unroll
-    for (int i = 0; i < kLead; ++i) fetch_next(p, prod, fq[i]);
+    for (int i = 0; i < kLead; ++i) fetch_next(p, prod, fq[i], head, lane, false);
     const int my_page = lane >> 2;
     const int my_part = lane & 3;
     const CUtensorMap* my_map = (my_part & 2) ? &vmap : &kmap;
-#if B200KV_DECODE_L2_PREFETCH > 0
     // Pull the first tiles towards L2 while the previous kernel is still finishing: L2 is the
     // point of coherence, so rows that kernel writes afterwards are still seen by the real loads.
 #pragma unroll
-    for (int i = 0; i < B200KV_DECODE_L2_PREFETCH; ++i) {
+    for (int i = 0; i < kL2PrefetchTiles; ++i) {
       const Fetch& f = fq[i];
       if (lane < 4 * f.npages) {
         int32_t id = f.id[0];
@@ -407,17 +535,40 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
           tma_prefetch_l2_3d(my_map, (my_part & 1) * 64, head, static_cast<int>(slot));
       }
     }
-#endif
-    pdl_wait_then_trigger();  // the pool may have been written by the previous kernel
+    pdl_wait_then_trigger();  // the pool and the new rows may have been written by the previous kernel
+#pragma unroll
+    for (int i = 0; i < kLead; ++i)
+      if (fq[i].app_b >= 0) load_new_row(p, fq[i], head, lane);
     const uint32_t my_off = my_page * kPageBytes + (my_part & 1) * (kPageBytes / 2) +
                             ((my_part & 2) ? kTileBytes : 0);
     for (int it = 0;; ++it) {
       const Fetch f = fq[0];
       if (f.ntok == 0) break;
       const int st = it % STAGES;
+      if (f.app_b >= 0) {
+        // Fused append: this tile holds the last page of its sequence, whose newest row is not in
+        // the pool yet.  Lanes 0..15 write the K row of this head, lanes 16..31 the V row, 16 bytes
+        // each; the proxy fence orders these generic stores before the bulk copies issued below.
+        int32_t last_id = f.id[0];
+#pragma unroll
+        for (int i = 1; i < kTilePages; ++i) last_id = (f.npages - 1 == i) ? f.id[i] : last_id;
+        const int64_t want = ((p.table_kind == B200KV_TABLE_BLOCK) ? static_cast<int64_t>(last_id) * kPS
+                                                                    : static_cast<int64_t>(last_id)) + f.app_off;
+        const int64_t slot = f.app_slot;
+        if (slot < 0 || slot >= p.pool_tokens) {
+          set_status(p.status, B200KV_DEV_BAD_SLOT);   // never dereferenced
+        } else {
+          if (slot != want) set_status(p.status, B200KV_DEV_BAD_SLOT);   // not this sequence's last position
+          __half* dst = (lane < 16 ? p.k_base : p.v_base) + slot * p.kv_tok_stride +
+                        static_cast<int64_t>(head) * p.kv_head_stride + (lane & 15) * 8;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(f.app_row0, f.app_row1, f.app_row2, f.app_row3);
+        }
+        asm volatile("fence.proxy.async.global;\n" ::: "memory");
+        __syncwarp();
+      }
       if (it >= STAGES && !mbar_wait_bounded(bar_empty + 8 * st, ((it / STAGES) - 1) & 1)) {
         set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-        break;  // consumers run into their own bounded waits and leave too
+        break;  // consumers run into their own bounded waits and stop computing too
       }
       const uint32_t full = bar_full + 8 * st;
       if (lane == 0)
@@ -439,15 +590,28 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
       }
 #pragma unroll
       for (int i = 0; i + 1 < kLead; ++i) fq[i] = fq[i + 1];
-      fetch_next(p, prod, fq[kLead - 1]);
+      fetch_next(p, prod, fq[kLead - 1], head, lane, true);
     }
     return;
   }
 
   // ================================= consumer warps =========================================
+  pdl_wait_then_trigger();  // q, the workspace and out belong to earlier kernels until here
+  if (team == 0 && any_empty) {
+    // No keys: the output rows are defined as zero, and nobody else writes them.
+    for (int b = 0; b < p.batch; ++b) {
+      if (seq_len_checked(p, b) != 0) continue;
+      for (int g = 0; g < p.group; ++g)
+        p.out[static_cast<int64_t>(b) * p.out_stride_b +
+              (static_cast<int64_t>(head) * p.group + g) * p.out_stride_h + tid] = __float2half_rn(0.f);
+    }
+  }
+  if (!has_range) return;
+
   Walker cons;
   cons.flat = r_begin;
   cons.flat_end = r_end;
+  cons.kseq = start_k;
   cons.enter(p, start_b, start_page);
 
   uint32_t qf[NB][8][2];  // Q^T as mma B fragments: 8 k-steps of 16 along head_dim
@@ -457,7 +621,6 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
   const int fcol = (lane & 3) * 2;   // fragment column pair: head within the N block
   const int mi = lane >> 3;          // which 8x8 matrix of an ldmatrix.x4 this lane addresses
   const int lrow = lane & 7;
-  pdl_wait_then_trigger();  // q, the workspace and out belong to earlier kernels until here
 
   // Q of one sequence as B fragments.  The next sequence's Q is requested when a piece ends, so
   // that its latency hides under the merge of that piece instead of in front of the next tile.
@@ -479,6 +642,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     }
   };
 
+  bool alive = true;   // false once a wait of this warp ran out: keep walking, stop computing
   Tile t;
   for (int it = 0; cons.next(p, t); ++it) {
     if (t.first) {
@@ -505,12 +669,12 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
     }
 
     const int st = it % STAGES;
-    if (!mbar_wait_bounded(bar_full + 8 * st, (it / STAGES) & 1)) {
+    if (alive && !mbar_wait_bounded(bar_full + 8 * st, (it / STAGES) & 1)) {
       set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
-      return;
+      alive = false;
     }
 
-    const int wtok = t.ntok - warp * kPS;  // valid tokens of this warp's page (may be <= 0)
+    const int wtok = alive ? t.ntok - warp * kPS : 0;  // valid tokens of this warp's page (may be <= 0)
     if (wtok > 0) {
       const uint32_t kpage = stage_base + st * kStageBytes + warp * kPageBytes;
       const uint32_t vpage = kpage + kTileBytes;
@@ -606,7 +770,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
       }
       // the merge buffer is shared by the four consumer warps: named barrier 1 (128 threads)
       // before it is rewritten and again before it is read
-      asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory");
+      consumer_bar();
       float* mo = merge_o + warp * kD * ROWS;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
@@ -630,7 +794,7 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
               make_float2(o[j][nb][2], o[j][nb][3]);
         }
       }
-      asm volatile("bar.sync 1, %0;\n" ::"n"(kConsumerWarps * 32) : "memory");
+      consumer_bar();
       const int64_t slot = (static_cast<int64_t>(team) + t.b) * p.kv_heads + head;
       // Thread = output column; its ROWS values of a warp's O are contiguous in the merge buffer
       // (vector loads), the (m, l) pairs are broadcast loads, and all rows are merged in registers.
@@ -683,163 +847,29 @@ paged_decode_split_kernel(DecodeParams p, const __grid_constant__ CUtensorMap km
           }
         }
       }
-    }
-  }
-}
-
-// Merge the split partials of each sequence: out = sum_p 2^(lse_p - M) o_p / sum_p 2^(lse_p - M)
-// (stage 2 of the reference, lite_llama/kernels/flashdecoding.py:199-267).  One CTA per
-// (sequence, KV head), one warp per query head of the group; every lane accumulates four output
-// columns over the pieces.  Up to four pieces: all loads issued together, one round trip.  More:
-// lanes hold the pieces' log-sum-exp values, maximum and weight sum are warp-shuffle reductions,
-// and the partial outputs are loaded eight pieces at a time.  Launched with programmatic stream serialisation: everything before
-// pdl_wait_then_trigger() (recomputing which teams touched this sequence) overlaps the tail
-// of the split kernel.
-template <int ROWS>
-__global__ void __launch_bounds__(kCombineThreads) decode_combine_kernel(DecodeParams p) {
-  __shared__ long long red[2][kCombineThreads / 32];
-  const int b = blockIdx.x / p.kv_heads;
-  const int kvh = blockIdx.x - b * p.kv_heads;
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-
-  // `before` in units (pages + kPieceCost per non-empty sequence, as in the split kernel);
-  // `total` carries the pages in its high half and the units in its low half
-  long long before = 0, total = 0;
-  const int nthreads = blockDim.x, nwarps = nthreads >> 5;
-  for (int i = tid; i < p.batch; i += nthreads) {
-    const int np = pages_of(seq_len_checked(p, i));
-    const int w = np + (np > 0 ? kPieceCost : 0);
-    total += (static_cast<long long>(np) << 32) + w;
-    if (i < b) before += w;
-  }
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) {
-    before += __shfl_xor_sync(0xffffffffu, before, d);
-    total += __shfl_xor_sync(0xffffffffu, total, d);
-  }
-  if (lane == 0) {
-    red[0][warp] = before;
-    red[1][warp] = total;
-  }
-  __syncthreads();
-  before = total = 0;
-  for (int w = 0; w < nwarps; ++w) {
-    before += red[0][w];
-    total += red[1][w];
-  }
-
-  const int len = seq_len_checked(p, b);
-  if (len == 0) {  // no keys: the output rows are defined as zero (nobody else writes them)
-    pdl_wait_then_trigger();
-    for (int i = tid; i < p.group * kD; i += nthreads) {
-      const int g = i / kD;
-      p.out[static_cast<int64_t>(b) * p.out_stride_b +
-            (static_cast<int64_t>(kvh) * p.group + g) * p.out_stride_h + (i - g * kD)] =
-          __float2half_rn(0.f);
-    }
-    return;
-  }
-  const int np = pages_of(len);
-  const long long total_pages = total >> 32, total_units = total & 0xffffffffll;
-  const int nteams_eff = effective_teams(p.nteams, total_pages);
-  const int t_first = team_of(before + kPieceCost, nteams_eff, total_units);
-  const int t_last = team_of(before + kPieceCost + np - 1, nteams_eff, total_units);
-  const int npieces = t_last - t_first + 1;
-  if (npieces == 1) return;  // the split kernel wrote the final rows itself
-
-  pdl_wait_then_trigger();  // partials of the split kernel are visible from here on
-
-  for (int g = warp; g < p.group; g += nwarps) {
-    const int hq = kvh * p.group + g;
-    if (npieces <= 4) {
-      // Common case: issue the loads of every piece's log-sum-exp AND output together, so the
-      // merge costs one memory round trip instead of two.
-      float lse[4];
-      float4 ov[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int64_t slot = (static_cast<int64_t>(t_first + min(j, npieces - 1)) + b) * p.kv_heads + kvh;
-        lse[j] = (j < npieces) ? p.part_lse[slot * ROWS + g] : -INFINITY;
-        ov[j] = *reinterpret_cast<const float4*>(p.part_o + (slot * ROWS + g) * kD + lane * 4);
-      }
-      const float M4 = fmaxf(fmaxf(lse[0], lse[1]), fmaxf(lse[2], lse[3]));
-      float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-      float wsum4 = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float w = (j < npieces) ? fast_exp2(lse[j] - M4) : 0.f;
-        wsum4 += w;
-        acc4.x += w * ov[j].x;
-        acc4.y += w * ov[j].y;
-        acc4.z += w * ov[j].z;
-        acc4.w += w * ov[j].w;
-      }
-      const float inv4 = 1.f / wsum4;
-      __half2 a01 = __floats2half2_rn(acc4.x * inv4, acc4.y * inv4);
-      __half2 a23 = __floats2half2_rn(acc4.z * inv4, acc4.w * inv4);
-      uint2 pk4;
-      pk4.x = *reinterpret_cast<uint32_t*>(&a01);
-      pk4.y = *reinterpret_cast<uint32_t*>(&a23);
-      *reinterpret_cast<uint2*>(p.out + static_cast<int64_t>(b) * p.out_stride_b +
-                                static_cast<int64_t>(hq) * p.out_stride_h + lane * 4) = pk4;
-      continue;
-    }
-    // More pieces (short shards of a long batch: few KV heads per GPU, many teams).  Lane i holds
-    // the log-sum-exp of piece p0 + i: the maximum and the weight sum are warp-shuffle reductions,
-    // and the weights reach the accumulating lanes by shuffle; the partial outputs are loaded
-    // eight pieces at a time, every load of a chunk issued before any arithmetic.
-    float M = -INFINITY;
-    for (int p0 = 0; p0 < npieces; p0 += 32) {
-      const int pc = p0 + lane;
-      if (pc < npieces) {
-        const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + kvh;
-        M = fmaxf(M, p.part_lse[slot * ROWS + g]);
-      }
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float wsum = 0.f;
-    for (int p0 = 0; p0 < npieces; p0 += 32) {
-      const int pc = p0 + lane;
-      float w = 0.f;
-      if (pc < npieces) {
-        const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + kvh;
-        w = fast_exp2(p.part_lse[slot * ROWS + g] - M);   // second read of the same line: a cache hit
-      }
-      wsum += w;
-      const int cnt = min(32, npieces - p0);
-      for (int j0 = 0; j0 < cnt; j0 += 8) {
-        float4 ov[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int64_t slot =
-              (static_cast<int64_t>(t_first + p0 + min(j0 + j, cnt - 1)) + b) * p.kv_heads + kvh;
-          ov[j] = *reinterpret_cast<const float4*>(p.part_o + (slot * ROWS + g) * kD + lane * 4);
+      if (!t.whole) {
+        // A partial: publish it, count it, and merge the sequence if it was the last one to arrive.
+        // The counter wraps to zero on the last arrival, so it needs no reset between launches.
+        __threadfence();
+        consumer_bar();
+        if (tid == 0) {
+          const int64_t u0 = t.units0 + p.piece_cost;
+          const int t_first = team_of(u0, nteams_eff, units_total);
+          const int t_last = team_of(u0 + t.np - 1, nteams_eff, units_total);
+          const int npieces = t_last - t_first + 1;
+          const unsigned old = atomicInc(p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head,
+                                         static_cast<unsigned>(npieces - 1));
+          verdict[0] = (old == static_cast<unsigned>(npieces - 1)) ? npieces : 0;
+          verdict[1] = t_first;
         }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float wj = __shfl_sync(0xffffffffu, w, (j0 + j) & 31);
-          if (j0 + j >= cnt) wj = 0.f;
-          acc.x += wj * ov[j].x;
-          acc.y += wj * ov[j].y;
-          acc.z += wj * ov[j].z;
-          acc.w += wj * ov[j].w;
+        consumer_bar();
+        const int npieces = verdict[0];
+        if (npieces > 0) {
+          __threadfence();
+          merge_pieces<ROWS>(p, t.b, head, verdict[1], npieces, tid);
         }
       }
     }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) wsum += __shfl_xor_sync(0xffffffffu, wsum, d);
-    const float inv = 1.f / wsum;
-    __half2 h01 = __floats2half2_rn(acc.x * inv, acc.y * inv);
-    __half2 h23 = __floats2half2_rn(acc.z * inv, acc.w * inv);
-    uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&h01);
-    pk.y = *reinterpret_cast<uint32_t*>(&h23);
-    *reinterpret_cast<uint2*>(p.out + static_cast<int64_t>(b) * p.out_stride_b +
-                              static_cast<int64_t>(hq) * p.out_stride_h + lane * 4) = pk;
   }
 }
 
@@ -850,16 +880,20 @@ inline int max_teams(int sms, int kv_heads) {
 }
 inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+// Tuning overrides (b200kv_set_option): 0 = automatic.
+int g_option_teams = 0;
+int g_option_piece_cost = 0;
+
 template <int ROWS, int STAGES>
 int launch_decode(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
-                  cudaStream_t stream) {
+                  bool programmatic, cudaStream_t stream) {
   constexpr int smem = STAGES * kStageBytes + kConsumerWarps * ROWS * kD * 4 +
                        kConsumerWarps * ROWS * 2 * 4 + (2 * STAGES + 2) * 8;
   static bool attr_done[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return record_cuda_error(cudaGetLastError());
   if (dev < 0 || dev >= 64 || !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(paged_decode_split_kernel<ROWS, STAGES>,
+    cudaError_t e = cudaFuncSetAttribute(paged_decode_kernel<ROWS, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return record_cuda_error(e);
     if (dev >= 0 && dev < 64) attr_done[dev] = true;
@@ -873,33 +907,34 @@ int launch_decode(const DecodeParams& p, const CUtensorMap& kmap, const CUtensor
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, paged_decode_split_kernel<ROWS, STAGES>, p, kmap, vmap);
-  if (e != cudaSuccess) return record_cuda_error(e);
-  int rc = check_launch();
-  if (rc != B200KV_OK) return rc;
-  cfg.gridDim = dim3(static_cast<unsigned>(p.batch * p.kv_heads));
-  // Few (sequence, KV head) CTAs (a shard with one or two KV heads): give each query head of the
-  // group its own warp; many CTAs: four warps keep the kernel's prologue short.
-  cfg.blockDim = dim3(p.batch * p.kv_heads < 128 ? kCombineThreads : kCombineThreads / 2);
-  cfg.dynamicSmemBytes = 0;
-  e = cudaLaunchKernelEx(&cfg, decode_combine_kernel<ROWS>, p);
+  cfg.numAttrs = programmatic ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, paged_decode_kernel<ROWS, STAGES>, p, kmap, vmap);
   if (e != cudaSuccess) return record_cuda_error(e);
   return check_launch();
 }
 
 }  // namespace
 
+int set_decode_option(int option, int64_t value) {
+  if (value < 0 || value > 65535) return B200KV_EINVAL;
+  switch (option) {
+    case B200KV_OPT_DECODE_TEAMS: g_option_teams = static_cast<int>(value); return B200KV_OK;
+    case B200KV_OPT_DECODE_PIECE_COST: g_option_piece_cost = static_cast<int>(value); return B200KV_OK;
+    default: return B200KV_EINVAL;
+  }
+}
+
 size_t decode_workspace_bytes(int batch, int q_heads, int kv_heads, int head_dim) {
   if (batch <= 0 || q_heads <= 0 || kv_heads <= 0 || head_dim != kD) return 0;
   if (q_heads % kv_heads != 0 || q_heads / kv_heads > 16) return 0;
+  if (static_cast<int64_t>(batch) * kv_heads > kMaxCounters) return 0;
   const int sms = device_sm_count();
   if (sms <= 0) return 0;
   const int rows = rows_for_group(q_heads / kv_heads);
   const size_t nslots = static_cast<size_t>(max_teams(sms, kv_heads)) + static_cast<size_t>(batch);
   const size_t po = align_up(nslots * kv_heads * rows * kD * sizeof(float), 256);
   const size_t pl = align_up(nslots * kv_heads * rows * sizeof(float), 256);
-  return po + pl;
+  return kCounterBytes + po + pl;
 }
 
 int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
@@ -913,13 +948,25 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   const int group = a.q_heads / a.kv_heads;
   if (group > 16) return B200KV_EUNSUPPORTED;
   if (a.batch > 4096) return B200KV_ETOOLARGE;
+  if (static_cast<int64_t>(a.batch) * a.kv_heads > kMaxCounters) return B200KV_ETOOLARGE;
   if (a.max_seq_len > (int64_t{1} << 30)) return B200KV_ETOOLARGE;
+  // The table must hold every row and every position the lengths can name.
+  if (a.table_rows <= 0 || a.table_cols <= 0 || a.table_row_stride < a.table_cols) return B200KV_EINVAL;
+  if (a.row_ids == nullptr && a.batch > a.table_rows) return B200KV_EINVAL;
+  const int64_t width_tokens = a.table_cols * (a.table_kind == B200KV_TABLE_BLOCK ? kPS : 1);
+  if (a.max_seq_len > width_tokens) return B200KV_EINVAL;
+  if ((a.new_kv == nullptr) != (a.slots == nullptr)) return B200KV_EINVAL;
+  if (a.flags & ~B200KV_DECODE_SERIALIZED) return B200KV_EINVAL;
   auto mis = [](const void* ptr, uintptr_t al) { return (reinterpret_cast<uintptr_t>(ptr) & (al - 1)) != 0; };
   if (mis(a.k_base, 16) || mis(a.v_base, 16) || mis(a.q, 4) || mis(a.out, 8) || mis(a.workspace, 16))
     return B200KV_EALIGN;
   if (a.kv_tok_stride % 8 != 0 || a.kv_head_stride % 8 != 0) return B200KV_EALIGN;
   if (a.q_stride_b % 2 != 0 || a.q_stride_h % 2 != 0) return B200KV_EALIGN;
   if (a.out_stride_b % 4 != 0 || a.out_stride_h % 4 != 0) return B200KV_EALIGN;
+  if (a.new_kv != nullptr) {
+    if (mis(a.new_kv, 16) || a.new_kv_tok_stride % 8 != 0) return B200KV_EALIGN;
+    if (a.new_kv_tok_stride < static_cast<int64_t>(2) * a.kv_heads * kD) return B200KV_EINVAL;
+  }
   const size_t need = decode_workspace_bytes(a.batch, a.q_heads, a.kv_heads, a.head_dim);
   if (need == 0) return B200KV_ECUDA;
   if (a.workspace_bytes < need) return B200KV_EWORKSPACE;
@@ -930,6 +977,7 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   // Do not launch more teams than the page bound can feed.
   const int64_t pages_bound = static_cast<int64_t>(a.batch) * ((a.max_seq_len + kPS - 1) / kPS);
   int64_t teams = pages_bound / kMinPagesPerTeam;
+  if (g_option_teams > 0 && teams > g_option_teams) teams = g_option_teams;
   if (teams > teams_cap) teams = teams_cap;
   if (teams < 1) teams = 1;
 
@@ -937,14 +985,15 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.q = static_cast<const __half*>(a.q);
   p.q_stride_b = a.q_stride_b;
   p.q_stride_h = a.q_stride_h;
-  p.k_base = static_cast<const __half*>(a.k_base);
-  p.v_base = static_cast<const __half*>(a.v_base);
+  p.k_base = static_cast<__half*>(const_cast<void*>(a.k_base));
+  p.v_base = static_cast<__half*>(const_cast<void*>(a.v_base));
   p.kv_tok_stride = a.kv_tok_stride;
   p.kv_head_stride = a.kv_head_stride;
   p.pool_tokens = a.pool_tokens;
   p.table = a.table;
   p.table_row_stride = a.table_row_stride;
   p.table_kind = a.table_kind;
+  p.table_rows = a.table_rows;
   p.row_ids = a.row_ids;
   p.seq_lens = a.seq_lens;
   p.seq_lens_i64 = a.seq_lens_i64;
@@ -955,9 +1004,15 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.max_seq_len = a.max_seq_len;
   p.nteams = static_cast<int>(teams);
+  p.piece_cost = g_option_piece_cost > 0 ? g_option_piece_cost : kDefaultPieceCost;
+  p.new_kv = static_cast<const __half*>(a.new_kv);
+  p.new_kv_tok_stride = a.new_kv_tok_stride;
+  p.slots = a.slots;
   const size_t nslots = static_cast<size_t>(teams_cap) + static_cast<size_t>(a.batch);
-  p.part_o = static_cast<float*>(a.workspace);
-  p.part_lse = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) +
+  uint8_t* ws = static_cast<uint8_t*>(a.workspace);
+  p.piece_ctr = reinterpret_cast<unsigned*>(ws);
+  p.part_o = reinterpret_cast<float*>(ws + kCounterBytes);
+  p.part_lse = reinterpret_cast<float*>(ws + kCounterBytes +
                                         align_up(nslots * a.kv_heads * rows * kD * sizeof(float), 256));
   p.out = static_cast<__half*>(a.out);
   p.out_stride_b = a.out_stride_b;
@@ -967,14 +1022,15 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   // TMA views of the K and V halves of the pool (d, head, token); one box = 16 token rows of
   // 64 halves, i.e. half a page of one head.
   CUtensorMap kmap, vmap;
-  int rc = encode_kv_tensor_map(&kmap, a.k_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+  int rc = cached_kv_tensor_map(&kmap, a.k_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
                                 a.kv_heads, kD, kPS);
   if (rc != B200KV_OK) return rc;
-  rc = encode_kv_tensor_map(&vmap, a.v_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+  rc = cached_kv_tensor_map(&vmap, a.v_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
                             a.kv_heads, kD, kPS);
   if (rc != B200KV_OK) return rc;
-  if (rows == 8) return launch_decode<8, kStagesRows8>(p, kmap, vmap, stream);
-  return launch_decode<16, 2>(p, kmap, vmap, stream);
+  const bool programmatic = (a.flags & B200KV_DECODE_SERIALIZED) == 0;
+  if (rows == 8) return launch_decode<8, kStagesRows8>(p, kmap, vmap, programmatic, stream);
+  return launch_decode<16, 2>(p, kmap, vmap, programmatic, stream);
 }
 
 // ---- decode on library-owned scratch (no allocation anywhere on the call path) -----------------
@@ -984,8 +1040,9 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
 // later cudaMalloc as a fault; a plug-in whose device memory is accounted for by the embedding
 // application; code running where the CUDA allocator must not be entered (a latency-critical
 // loop that cannot afford the device-wide synchronisation cudaMalloc / cudaFree imply).  For them
-// the split-KV partials live in this file-scope device array instead.  Every GPU that loads the
-// library holds these bytes until the process exits, which is why the size is modest and fixed.
+// the split-KV partials and the arrival counters live in this file-scope device array instead.
+// Every GPU that loads the library holds these bytes until the process exits, which is why the
+// size is modest and fixed.  The array starts zero-filled, which is the state the counters need.
 constexpr size_t kStaticScratchBytes = B200KV_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
 

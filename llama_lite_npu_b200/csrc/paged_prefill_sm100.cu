@@ -176,6 +176,8 @@ struct PrefillParams {
   const int32_t* table;
   int64_t table_row_stride;
   int table_kind;
+  int table_rows;
+  int64_t table_tokens;   // positions a table row can name (dense: tokens addressable from K/V)
   const int32_t* req_ids;
   const int32_t* q_start;
   const void* ctx_lens;
@@ -212,12 +214,26 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const int b = blockIdx.z;
   const int64_t q_len = load_len(p.q_lens, p.lens_i64, b);
   const int64_t ctx = load_len(p.ctx_lens, p.lens_i64, b);
-  if (q_len < 0 || ctx < 0) {
+  // Every early exit below still makes the programmatic-launch calls, so that a dependent kernel
+  // can rely on "my predecessor waited for its own predecessor".
+  auto leave_early = [] {
+    cudaGridDependencySynchronize();
+    cudaTriggerProgrammaticLaunchCompletion();
+  };
+  const int table_row = p.req_ids ? __ldg(p.req_ids + b) : b;
+  // A stale length or request id must not become a read outside the table: such a request is
+  // reported and skipped.
+  if (q_len < 0 || ctx < 0 || q_len > p.total_q || ctx > p.table_tokens || ctx + q_len > p.table_tokens ||
+      (p.table_kind != B200KV_TABLE_DENSE && (table_row < 0 || table_row >= p.table_rows))) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
+    leave_early();
     return;
   }
   const int t_b = static_cast<int>((q_len + kBM - 1) / kBM);   // query tiles of the request
-  if (pair_k > t_b - 1 - pair_k) return;                        // also q_len == 0
+  if (pair_k > t_b - 1 - pair_k) {                              // also q_len == 0
+    leave_early();
+    return;
+  }
   const int n_work = pair_k < t_b - 1 - pair_k ? 2 : 1;
   const int64_t q_start_b = static_cast<int64_t>(__ldg(p.q_start + b));
   struct Work {
@@ -241,9 +257,9 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   const Work work0 = work_of(0), work1 = work_of(n_work - 1);
   if (work0.q_tok0 < 0 || work0.q_tok0 + work0.rows > p.total_q || work1.q_tok0 < 0) {
     set_status(p.status, B200KV_DEV_BAD_LENGTH);
+    leave_early();
     return;
   }
-  const int table_row = p.req_ids ? __ldg(p.req_ids + b) : b;
 
   // ---- shared memory carve-up -----------------------------------------------------------------
   const uint32_t sm_q = smem_u32(smem);                     // [group][32 KB]
@@ -262,6 +278,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
   static_assert(8 + 2 * 8 * kSlots + 4 * 8 * kGroups + 8 + 8 <= kBarBytes, "barrier area too small");
   if ((sm_q & 1023u) != 0) {  // swizzled boxes and UMMA descriptors assume 1024-byte alignment
     set_status(p.status, B200KV_DEV_BAD_PAGE);
+    leave_early();
     return;
   }
 
@@ -508,13 +525,16 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
     const uint32_t b_sfull = bar_sfull + 8 * g, b_pfull = bar_pfull + 8 * g, b_pvfull = bar_pvfull + 8 * g;
     bool ok = true;
     int tile_base = 0, item_base = 0;
-    for (int w = 0; active && ok && w < n_work; ++w) {
+    // A warp whose wait ran out (ok == false) stops computing but keeps visiting its query tiles,
+    // so that it still meets the other warps of its group at the two named barriers of each
+    // read-out: nobody is left waiting at a barrier for a warp that has gone.
+    for (int w = 0; active && w < n_work; ++w) {
     const Work wk = w ? work1 : work0;
     const int n_tiles = wk.n_tiles;
     const int64_t row0 = wk.row0, kv_len = wk.kv_len;
     const int64_t q_pos = ctx + row0 + row;                // logical position of this query row
     float m_used = -INFINITY, l_run = 0.f;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = 0; ok && j < n_tiles; ++j) {
       const uint32_t par = (tile_base + j) & 1;            // phase of the per-key-tile barriers
       if (!mbar_wait_bounded(b_sfull, par)) { ok = false; break; }
       tc_fence_after();
@@ -629,7 +649,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
     }
     // ---- the query tile's rows: O / l, once its last P V has completed -----------------------
     if (ok && !mbar_wait_bounded(b_pvfull, (tile_base + n_tiles - 1) & 1)) ok = false;
-    if (ok) {
+    {
       tc_fence_after();
       const float inv = 1.f / l_run;
       const int rows = wk.rows;
@@ -662,7 +682,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
       for (int it = 0; it < kBM * 16 / (kGroupWarps * 32); ++it) {
         const int idx = it * (kGroupWarps * 32) + gtid;    // half a warp per row
         const int r = idx >> 4, c = idx & 15;
-        if (r < rows) {
+        if (ok && r < rows) {
           uint4 v;
           asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];\n"
                        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
@@ -694,7 +714,7 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
 // box = 64 halves x 1 head x 128 tokens (one half of a query tile), 128-byte swizzle.
 int encode_q_tensor_map(CUtensorMap* out, const void* q, int64_t total_q, int64_t stride_t,
                         int64_t stride_h, int heads) {
-  return encode_kv_tensor_map(out, q, total_q, stride_t, stride_h, heads, kD, kBM);
+  return cached_kv_tensor_map(out, q, total_q, stride_t, stride_h, heads, kD, kBM);
 }
 
 }  // namespace
@@ -708,7 +728,10 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   if (a.table_kind != B200KV_TABLE_BLOCK && a.table_kind != B200KV_TABLE_TOKEN &&
       a.table_kind != B200KV_TABLE_DENSE)
     return B200KV_EINVAL;
-  if (a.table_kind != B200KV_TABLE_DENSE && !a.table) return B200KV_EINVAL;
+  if (a.table_kind != B200KV_TABLE_DENSE &&
+      (!a.table || a.table_rows <= 0 || a.table_cols <= 0 || a.table_row_stride < a.table_cols))
+    return B200KV_EINVAL;
+  if (a.table_kind != B200KV_TABLE_DENSE && a.req_ids == nullptr && a.batch > a.table_rows) return B200KV_EINVAL;
   if (a.head_dim != kD || a.page_size != kPS) return B200KV_EUNSUPPORTED;
   if (a.q_heads % a.kv_heads != 0) return B200KV_EUNSUPPORTED;
   if (a.batch > 65535 || a.q_heads > 65535 * 16) return B200KV_ETOOLARGE;
@@ -720,10 +743,10 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   CUtensorMap qmap, kmap, vmap;
   int rc = encode_q_tensor_map(&qmap, a.q, a.total_q, a.q_stride_t, a.q_stride_h, a.q_heads);
   if (rc != B200KV_OK) return rc;
-  rc = encode_kv_tensor_map(&kmap, a.k_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+  rc = cached_kv_tensor_map(&kmap, a.k_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
                             a.kv_heads, kD, kPS);
   if (rc != B200KV_OK) return rc;
-  rc = encode_kv_tensor_map(&vmap, a.v_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
+  rc = cached_kv_tensor_map(&vmap, a.v_base, a.pool_tokens, a.kv_tok_stride, a.kv_head_stride,
                             a.kv_heads, kD, kPS);
   if (rc != B200KV_OK) return rc;
 
@@ -731,6 +754,9 @@ int paged_prefill(const PrefillArgs& a, cudaStream_t stream) {
   p.table = a.table;
   p.table_row_stride = a.table_row_stride;
   p.table_kind = a.table_kind;
+  p.table_rows = a.table_rows;
+  p.table_tokens = a.table_kind == B200KV_TABLE_DENSE ? a.pool_tokens
+                   : a.table_cols * (a.table_kind == B200KV_TABLE_BLOCK ? kPS : 1);
   p.req_ids = a.req_ids;
   p.q_start = a.q_start;
   p.ctx_lens = a.ctx_lens;

@@ -17,6 +17,12 @@ int encode_kv_tensor_map(CUtensorMap* out, const void* base, int64_t pool_tokens
                          int64_t tok_stride, int64_t head_stride, int n_heads, int head_dim,
                          int box_tokens);
 
+// Same map through a small per-process cache keyed by every argument: encoding costs a driver
+// call, and a serving loop passes the same few pool views (one per layer) on every step.
+int cached_kv_tensor_map(CUtensorMap* out, const void* base, int64_t pool_tokens,
+                         int64_t tok_stride, int64_t head_stride, int n_heads, int head_dim,
+                         int box_tokens);
+
 #ifdef __CUDACC__
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t t;

@@ -26,6 +26,10 @@ from . import _lib
 TABLE_BLOCK = 0
 TABLE_TOKEN = 1
 TABLE_DENSE = 2
+DECODE_SERIALIZED = 1          # B200KV_DECODE_SERIALIZED
+DECODE_COUNTER_BYTES = 256 << 10
+OPT_DECODE_TEAMS = 1
+OPT_DECODE_PIECE_COST = 2
 
 _TABLE_KINDS = {"block": TABLE_BLOCK, "token": TABLE_TOKEN, "dense": TABLE_DENSE}
 
@@ -62,6 +66,10 @@ def check_status(device_index: Optional[int] = None) -> None:
     code = int(st.item())
     if code != 0:
         st.zero_()
+        if code == 104:   # a wait ran out: the decode workspace's arrival counters may be off
+            ws = _workspace.get(device_index)
+            if ws is not None:
+                ws[:DECODE_COUNTER_BYTES].zero_()
         raise RuntimeError(f"b200kv device status {code}: {_lib.strerror(code)}")
 
 
@@ -117,8 +125,8 @@ def _kv_views(k_cache: torch.Tensor, v_cache: torch.Tensor):
 
 
 def decode_workspace(device_index: int, batch: int, q_heads: int, kv_heads: int, head_dim: int):
-    """Per-device scratch for split-KV partials; grown on demand, never shrunk, so its
-    address is stable across calls of the same or a smaller shape."""
+    """Per-device scratch for the decode kernel (arrival counters + split-KV partials); grown on
+    demand, never shrunk, so its address is stable across calls of the same or a smaller shape."""
     key = (device_index, batch, q_heads, kv_heads, head_dim)
     need = _workspace_need.get(key)
     if need is None:
@@ -133,7 +141,9 @@ def decode_workspace(device_index: int, batch: int, q_heads: int, kv_heads: int,
     if ws is None or ws.numel() < need:
         if ws is not None:
             _retired_workspaces.append(ws)   # captured CUDA graphs may still point into it
-        ws = torch.empty(need, dtype=torch.uint8, device=f"cuda:{device_index}")
+        # zero-filled: the arrival counters at its start must be zero before the first call, and
+        # every call leaves them at zero
+        ws = torch.zeros(need, dtype=torch.uint8, device=f"cuda:{device_index}")
         _workspace[device_index] = ws
     return ws
 
@@ -343,7 +353,68 @@ def fused_qk_norm_rope_append(xq: torch.Tensor, xkv: torch.Tensor, q_norm_weight
     return out
 
 
-@torch.no_grad()
+def _decode_call(new_kv, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, max_actual_seq_len,
+                 b_req_idx, table_kind, page_size, out, metadata_fresh):
+    dev = _device_index(q)
+    _require(q.dtype == torch.float16 and q.dim() == 3, "q must be float16 [batch, heads, head_dim]")
+    assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
+    batch, q_heads, d = q.shape
+    q_sb, q_sh, q_sd = q.stride()
+    _require(q_sd == 1, "q must be contiguous along head_dim")
+    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
+    kv_heads = k_cache.shape[1]
+    kind = _TABLE_KINDS[table_kind]
+    _require(kind in (TABLE_BLOCK, TABLE_TOKEN), "decode takes a 'token' or 'block' table")
+    _require(tbl.dtype == torch.int32 and tbl.dim() == 2 and tbl.stride(1) == 1,
+             "the table must be a 2-D int32 tensor contiguous along its last dimension")
+    tbl_rows, tbl_cols = tbl.shape
+    _require(b_seq_len.shape[0] == batch, "b_seq_len must have one entry per batch row")
+    lens_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
+    rows_ptr = 0
+    if b_req_idx is not None:
+        _require(b_req_idx.dtype == torch.int32 and b_req_idx.shape == (batch,)
+                 and b_req_idx.is_contiguous(), "b_req_idx must be contiguous int32 [batch]")
+        rows_ptr = b_req_idx.data_ptr()
+    else:
+        _require(tbl_rows >= batch, "the table has fewer rows than the batch")
+    width_tokens = tbl_cols * (page_size if kind == TABLE_BLOCK else 1)
+    max_len = int(max_actual_seq_len)
+    _require(0 <= max_len <= width_tokens, "max_actual_seq_len exceeds the table width")
+    if out is None:
+        out = torch.empty_like(q)
+    else:
+        _require(out.shape == q.shape and out.dtype == torch.float16 and out.stride(2) == 1,
+                 "out must match q")
+    if batch == 0:
+        return out
+    ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
+    flags = DECODE_SERIALIZED if metadata_fresh else 0
+    lib = _lib.lib()
+    with _on_device(dev):
+        if new_kv is None:
+            rc = lib.b200kv_paged_decode(
+                q.data_ptr(), q_sb, q_sh,
+                k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
+                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr, lens_ptr, lens_i64,
+                batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
+                ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
+                flags, status_tensor(dev).data_ptr(), _stream(dev),
+            )
+        else:
+            rc = lib.b200kv_append_paged_decode(
+                new_kv.data_ptr(), new_kv.stride(0), slots.data_ptr(),
+                q.data_ptr(), q_sb, q_sh,
+                k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
+                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr, lens_ptr, lens_i64,
+                batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
+                ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
+                flags, status_tensor(dev).data_ptr(), _stream(dev),
+            )
+    _lib.check(rc)
+    _after_call(dev)
+    return out
+
+
 def flash_decoding(
     q: torch.Tensor,
     k_cache: torch.Tensor,
@@ -357,6 +428,7 @@ def flash_decoding(
     table_kind: str = "token",
     page_size: int = 16,
     out: Optional[torch.Tensor] = None,
+    metadata_fresh: bool = False,
 ) -> torch.Tensor:
     """Paged decode attention; returns a new ``[batch, q_heads, head_dim]`` fp16 tensor.
 
@@ -369,56 +441,61 @@ def flash_decoding(
 
     Keyword extensions: ``b_req_idx`` (int32 ``[batch]``) selects table rows explicitly, which
     a continuous batch with gaps needs; ``table_kind="block"`` passes a page-id table
-    ``[rows, max_pages]`` instead of a token table.
+    ``[rows, max_pages]`` instead of a token table; ``metadata_fresh=True`` must be passed when
+    ``b_seq_len``, ``b_req_idx`` or the table were written by the kernel launched immediately
+    before this call on the same stream (the launch then gives up its overlap with that kernel).
     """
-    dev = _device_index(q)
-    _require(q.dtype == torch.float16 and q.dim() == 3, "q must be float16 [batch, heads, head_dim]")
-    assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
-    _require(q.stride(2) == 1, "q must be contiguous along head_dim")
-    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
-    batch, q_heads, d = q.shape
-    kv_heads = k_cache.shape[1]
-    kind = _TABLE_KINDS[table_kind]
-    _require(kind in (TABLE_BLOCK, TABLE_TOKEN), "decode takes a 'token' or 'block' table")
-    tbl = b_req_tokens_table
-    _require(tbl.dtype == torch.int32 and tbl.dim() == 2 and tbl.stride(1) == 1,
-             "the table must be a 2-D int32 tensor contiguous along its last dimension")
-    _require(b_seq_len.shape[0] == batch, "b_seq_len must have one entry per batch row")
-    lens_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
-    rows_ptr = 0
-    if b_req_idx is not None:
-        _require(b_req_idx.dtype == torch.int32 and b_req_idx.shape == (batch,)
-                 and b_req_idx.is_contiguous(), "b_req_idx must be contiguous int32 [batch]")
-        rows_ptr = b_req_idx.data_ptr()
-    else:
-        _require(tbl.shape[0] >= batch, "the table has fewer rows than the batch")
-    width_tokens = tbl.shape[1] * (page_size if kind == TABLE_BLOCK else 1)
-    max_len = int(max_actual_seq_len)
-    _require(0 <= max_len <= width_tokens, "max_actual_seq_len exceeds the table width")
-    if out is None:
-        out = torch.empty_like(q)
-    else:
-        _require(out.shape == q.shape and out.dtype == torch.float16 and out.stride(2) == 1,
-                 "out must match q")
-    if batch == 0:
-        return out
-    ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
-    with _on_device(dev):
-        rc = _lib.lib().b200kv_paged_decode(
-            q.data_ptr(), q.stride(0), q.stride(1),
-            k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
-            tbl.data_ptr(), tbl.stride(0), kind, rows_ptr, lens_ptr, lens_i64,
-            batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
-            ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
-            status_tensor(dev).data_ptr(), _stream(dev),
-        )
-    _lib.check(rc)
-    _after_call(dev)
-    return out
+    return _decode_call(None, None, q, k_cache, v_cache, qk_scale, b_req_tokens_table, b_seq_len,
+                        max_actual_seq_len, b_req_idx, table_kind, page_size, out, metadata_fresh)
 
 
-def _prefill_call(q, k_cache, v_cache, scale_log2, tbl_ptr, tbl_stride, kind, req_ids_ptr,
-                  q_start_loc, ctx_ptr, qlen_ptr, lens_i64, batch, max_q_len, page_size):
+def append_flash_decoding(
+    KV_Values: torch.Tensor,
+    Select_Index: torch.Tensor,
+    KV_Buffer: torch.Tensor,
+    q: torch.Tensor,
+    qk_scale: float,
+    b_req_tokens_table: torch.Tensor,
+    b_seq_len: torch.Tensor,
+    max_actual_seq_len: int,
+    *,
+    b_req_idx: Optional[torch.Tensor] = None,
+    table_kind: str = "token",
+    page_size: int = 16,
+    out: Optional[torch.Tensor] = None,
+    metadata_fresh: bool = False,
+) -> torch.Tensor:
+    """One decode step of one layer in one launch: ``update_kv_buffer(KV_Values, Select_Index,
+    KV_Buffer)`` followed by ``flash_decoding(q, KV_Buffer[:, :kv_heads], KV_Buffer[:, kv_heads:],
+    ...)``, the pair ``Attention.token_forward`` issues (``lite_llama/models/qwen3.py:62-74``).
+
+    ``KV_Values`` is ``[batch, 2*kv_heads, head_dim]``, ``Select_Index[b]`` the slot of sequence
+    ``b``'s newest token (position ``b_seq_len[b] - 1``, the lengths already count it).  The pool
+    rows are written bit-exactly; the other arguments are those of :func:`flash_decoding`."""
+    _require(KV_Buffer.dim() == 3 and KV_Buffer.dtype == torch.float16 and KV_Buffer.shape[1] % 2 == 0,
+             "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
+    rows, d = KV_Buffer.shape[1], KV_Buffer.shape[2]
+    batch = q.shape[0]
+    _require(KV_Values.dtype == torch.float16 and KV_Values.shape == (batch, rows, d)
+             and KV_Values.stride(2) == 1 and KV_Values.stride(1) == d and KV_Values.device == KV_Buffer.device,
+             "KV_Values must be float16 [batch, 2*kv_heads, head_dim] on the pool's device, contiguous inside a token")
+    _require(Select_Index.dtype == torch.int32 and Select_Index.shape == (batch,) and Select_Index.is_contiguous()
+             and Select_Index.device == KV_Buffer.device, "Select_Index must be contiguous int32 [batch]")
+    _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d, "KV_Buffer must be contiguous inside a token")
+    kvh = rows // 2
+    return _decode_call(KV_Values, Select_Index, q, KV_Buffer[:, :kvh], KV_Buffer[:, kvh:], qk_scale,
+                        b_req_tokens_table, b_seq_len, max_actual_seq_len, b_req_idx, table_kind,
+                        page_size, out, metadata_fresh)
+
+
+def set_decode_option(option: int, value: int) -> None:
+    """Tuning override of the decode launch (``OPT_DECODE_TEAMS`` / ``OPT_DECODE_PIECE_COST``);
+    0 restores the automatic choice."""
+    _lib.check(_lib.lib().b200kv_set_option(int(option), int(value)))
+
+
+def _prefill_call(q, k_cache, v_cache, scale_log2, tbl_ptr, tbl_stride, kind, tbl_rows, tbl_cols,
+                  req_ids_ptr, q_start_loc, ctx_ptr, qlen_ptr, lens_i64, batch, max_q_len, page_size):
     dev = _device_index(q)
     tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
     total_q, q_heads, d = q.shape
@@ -430,7 +507,7 @@ def _prefill_call(q, k_cache, v_cache, scale_log2, tbl_ptr, tbl_stride, kind, re
         rc = _lib.lib().b200kv_paged_prefill(
             q.data_ptr(), q.stride(0), q.stride(1),
             k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
-            tbl_ptr, tbl_stride, kind, req_ids_ptr, q_start_loc.data_ptr(),
+            tbl_ptr, tbl_stride, kind, tbl_rows, tbl_cols, req_ids_ptr, q_start_loc.data_ptr(),
             ctx_ptr, qlen_ptr, lens_i64, batch, total_q, int(max_q_len),
             q_heads, kv_heads, d, int(page_size), float(scale_log2),
             output.data_ptr(), output.stride(0), output.stride(1),
@@ -480,8 +557,8 @@ def paged_chunk_flash_attention(
     ctx_ptr, lens_i64 = _lens_arg(context_lens, "context_lens")
     qlen_ptr, _ = _lens_arg(q_seq_lens, "q_seq_lens")
     return _prefill_call(q, k_cache, v_cache, sm_scale, tbl.data_ptr(), tbl.stride(0), kind,
-                         req_ids.data_ptr(), q_start_loc, ctx_ptr, qlen_ptr, lens_i64, batch,
-                         max_q_len, page_size)
+                         tbl.shape[0], tbl.shape[1], req_ids.data_ptr(), q_start_loc, ctx_ptr, qlen_ptr,
+                         lens_i64, batch, max_q_len, page_size)
 
 
 @torch.no_grad()
@@ -507,7 +584,7 @@ def flash_attention2_no_pad(
              and b_start_loc.is_contiguous(), "b_start_loc must be contiguous int32 [batch]")
     qlen_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
     zeros = torch.zeros_like(b_seq_len)
-    return _prefill_call(q, k, v, sm_scale, 0, 0, TABLE_DENSE, 0, b_start_loc,
+    return _prefill_call(q, k, v, sm_scale, 0, 0, TABLE_DENSE, 0, 0, 0, b_start_loc,
                          zeros.data_ptr(), qlen_ptr, lens_i64, batch, max_seq_len, 16)
 
 
@@ -515,6 +592,7 @@ __all__ = [
     "update_kv_buffer",
     "update_kv_buffer_split",
     "flash_decoding",
+    "append_flash_decoding",
     "paged_chunk_flash_attention",
     "flash_attention2_no_pad",
     "check_status",

@@ -288,6 +288,15 @@ class PrefillCase:
         return 4 * c.head_dim * c.q_heads * pairs
 
 
+def draw_prefill_lengths(cfg: PrefillConfig):
+    """(prompt lengths, shared prefix pages) of a prefill configuration, without building it."""
+    ps = cfg.page_size
+    prompt_lens = hash_randint(cfg.seed, cfg.batch, cfg.prompt_lo, cfg.prompt_hi, stream=1)
+    f = hash_uniform(cfg.seed, cfg.batch, stream=6) * cfg.shared_frac_hi
+    shared = np.floor(f * ((prompt_lens + ps - 1) // ps)).astype(np.int64)
+    return prompt_lens, np.minimum(shared, (prompt_lens - 1) // ps)
+
+
 def make_prefill_case(cfg: PrefillConfig, device="cpu", fill="hash",
                       prompt_lens: Optional[np.ndarray] = None,
                       shared_pages: Optional[np.ndarray] = None) -> PrefillCase:
@@ -295,13 +304,18 @@ def make_prefill_case(cfg: PrefillConfig, device="cpu", fill="hash",
     already in the pool (and hold a second reference); the rest of the prompt is the query
     chunk whose K/V the step appends before attending."""
     ps = cfg.page_size
-    if prompt_lens is None:
-        prompt_lens = hash_randint(cfg.seed, cfg.batch, cfg.prompt_lo, cfg.prompt_hi, stream=1)
+    if prompt_lens is None or shared_pages is None:
+        drawn_lens, drawn_shared = draw_prefill_lengths(cfg)
+        if prompt_lens is None:
+            prompt_lens = drawn_lens
+            if shared_pages is None:
+                shared_pages = drawn_shared
+        else:
+            prompt_lens = np.asarray(prompt_lens, dtype=np.int64)
+            f = hash_uniform(cfg.seed, cfg.batch, stream=6) * cfg.shared_frac_hi
+            shared_pages = np.floor(f * ((prompt_lens + ps - 1) // ps)).astype(np.int64)
     prompt_lens = np.asarray(prompt_lens, dtype=np.int64)
     total_pages = (prompt_lens + ps - 1) // ps
-    if shared_pages is None:
-        f = hash_uniform(cfg.seed, cfg.batch, stream=6) * cfg.shared_frac_hi
-        shared_pages = np.floor(f * total_pages).astype(np.int64)
     shared_pages = np.minimum(np.asarray(shared_pages, dtype=np.int64), (prompt_lens - 1) // ps)
     ctx = shared_pages * ps
     qn = prompt_lens - ctx

@@ -101,9 +101,10 @@ def test_kernel_reproduces_reference_decode_metadata(recorded, built_lib):
         for r, row in zip(recorded["batch"], recorded["token_rows"]):
             assert d_tokens[r, : len(row)].tolist() == row
         kernels.check_status(0)
-    # a sequence whose next page is not in the table: refused, nothing written for it
+    # a sequence whose next page is not in the table: refused; its slot becomes -1 (the append skips
+    # negative slots) instead of keeping the previous step's slot
     lens = torch.tensor([4, 3], dtype=torch.int32, device=dev)
-    slots = torch.full((2,), -1, dtype=torch.int32, device=dev)
+    slots = torch.full((2,), 77, dtype=torch.int32, device=dev)    # stale slots of the previous step
     tbl = torch.tensor([[5, 0], [6, 0]], dtype=torch.int32, device=dev)
     kernels.advance_decode_metadata(lens, slots, tbl, 4, 8, page_counts=torch.tensor([1, 1], dtype=torch.int32, device=dev))
     with pytest.raises(RuntimeError, match="length"):
