@@ -297,60 +297,81 @@ __device__ __forceinline__ void consumer_bar() {
 
 // Merge the `npieces` partials of (sequence b, KV head `head`) held in slots t_first + b ...:
 // out = sum_p 2^(lse_p - M) o_p / sum_p 2^(lse_p - M).  Run by the 128 consumer threads of the CTA
-// that delivered the last partial; thread = output column, rows eight at a time, the loads of
-// kMergeBatch pieces in flight together.  The partials were written by other CTAs: read them past L1.
-constexpr int kMergeBatch = 2;
+// that delivered the last partial; everything it reads was written by other CTAs, so the loads go
+// past L1, and the whole merge costs about three memory round trips whatever the piece count:
+//   A. thread (piece j, row r) fetches lse[j][r] (128 / ROWS pieces per sweep) into shared memory
+//      and the row maxima are reduced with shuffles and one pass through shared memory;
+//   B. the same threads turn their entries into weights 2^(lse - M) in place and reduce the row sums;
+//   C. thread = output column: the partial outputs are loaded kMergeBatch pieces at a time, every
+//      load of a batch issued before any arithmetic, and weighted with the shared-memory weights.
+// `wbuf` (npieces * ROWS floats) and `red` (2 * 4 * ROWS floats) are shared-memory scratch that
+// nobody else uses between the surrounding consumer barriers.
+constexpr int kMergeBatch = 6;
 template <int ROWS>
 __device__ __forceinline__ void merge_pieces(const DecodeParams& p, int b, int head, int t_first,
-                                             int npieces, int tid) {
+                                             int npieces, int tid, float* wbuf, float* red) {
+  constexpr int kPerSweep = kConsumerThreads / ROWS;
+  const int my_r = tid % ROWS;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  auto slot_of = [&](int pc) { return (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head; };
+  // ---- A: log-sum-exp values -> shared memory, row maxima --------------------------------------
+  float m = -INFINITY;
+  for (int j = tid / ROWS; j < npieces; j += kPerSweep) {
+    const float v = __ldcg(p.part_lse + slot_of(j) * ROWS + my_r);
+    wbuf[j * ROWS + my_r] = v;
+    m = fmaxf(m, v);
+  }
+#pragma unroll
+  for (int d = ROWS; d < 32; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if (lane < ROWS) red[warp * ROWS + lane] = m;
+  consumer_bar();
+  const float M = fmaxf(fmaxf(red[my_r], red[ROWS + my_r]), fmaxf(red[2 * ROWS + my_r], red[3 * ROWS + my_r]));
+  // ---- B: weights in place, row sums --------------------------------------------------------------
+  float sum = 0.f;
+  for (int j = tid / ROWS; j < npieces; j += kPerSweep) {
+    const float w = fast_exp2(wbuf[j * ROWS + my_r] - M);
+    wbuf[j * ROWS + my_r] = w;
+    sum += w;
+  }
+#pragma unroll
+  for (int d = ROWS; d < 32; d <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+  float* red_sum = red + kConsumerWarps * ROWS;
+  if (lane < ROWS) red_sum[warp * ROWS + lane] = sum;
+  consumer_bar();
+  // ---- C: weighted sum of the partial outputs, thread = column -----------------------------------
 #pragma unroll 1
   for (int r0 = 0; r0 < ROWS && r0 < p.group; r0 += 8) {
-    float M[8], L[8], acc[8];
+    float acc[8];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) {
-      M[r] = -INFINITY;
-      L[r] = acc[r] = 0.f;
-    }
-#pragma unroll 1
-    for (int pc = 0; pc < npieces; ++pc) {
-      const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head;
-      const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0));
-      const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0 + 4));
-      M[0] = fmaxf(M[0], a.x); M[1] = fmaxf(M[1], a.y); M[2] = fmaxf(M[2], a.z); M[3] = fmaxf(M[3], a.w);
-      M[4] = fmaxf(M[4], c.x); M[5] = fmaxf(M[5], c.y); M[6] = fmaxf(M[6], c.z); M[7] = fmaxf(M[7], c.w);
-    }
+    for (int r = 0; r < 8; ++r) acc[r] = 0.f;
 #pragma unroll 1
     for (int p0 = 0; p0 < npieces; p0 += kMergeBatch) {
-      float lse[kMergeBatch][8], ov[kMergeBatch][8];
+      float ov[kMergeBatch][8];
 #pragma unroll
       for (int j = 0; j < kMergeBatch; ++j) {
-        const int pc = min(p0 + j, npieces - 1);
-        const int64_t slot = (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head;
-        const float4 a = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0));
-        const float4 c = __ldcg(reinterpret_cast<const float4*>(p.part_lse + slot * ROWS + r0 + 4));
-        lse[j][0] = a.x; lse[j][1] = a.y; lse[j][2] = a.z; lse[j][3] = a.w;
-        lse[j][4] = c.x; lse[j][5] = c.y; lse[j][6] = c.z; lse[j][7] = c.w;
+        const int64_t slot = slot_of(min(p0 + j, npieces - 1));
 #pragma unroll
         for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
       }
 #pragma unroll
       for (int j = 0; j < kMergeBatch; ++j) {
         if (p0 + j < npieces) {
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const float w = fast_exp2(lse[j][r] - M[r]);
-            L[r] += w;
-            acc[r] += w * ov[j][r];
-          }
+          const float4 w0 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0);
+          const float4 w1 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0 + 4);
+          acc[0] += w0.x * ov[j][0]; acc[1] += w0.y * ov[j][1]; acc[2] += w0.z * ov[j][2]; acc[3] += w0.w * ov[j][3];
+          acc[4] += w1.x * ov[j][4]; acc[5] += w1.y * ov[j][5]; acc[6] += w1.z * ov[j][6]; acc[7] += w1.w * ov[j][7];
         }
       }
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
-      if (r0 + r < p.group)
+      if (r0 + r < p.group) {
+        const float L = red_sum[r0 + r] + red_sum[ROWS + r0 + r] + red_sum[2 * ROWS + r0 + r] + red_sum[3 * ROWS + r0 + r];
         p.out[static_cast<int64_t>(b) * p.out_stride_b +
               (static_cast<int64_t>(head) * p.group + r0 + r) * p.out_stride_h + tid] =
-            __float2half_rn(acc[r] / L[r]);
+            __float2half_rn(acc[r] / L);
+      }
     }
   }
 }
@@ -866,7 +887,7 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
         const int npieces = verdict[0];
         if (npieces > 0) {
           __threadfence();
-          merge_pieces<ROWS>(p, t.b, head, verdict[1], npieces, tid);
+          merge_pieces<ROWS>(p, t.b, head, verdict[1], npieces, tid, merge_o, merge_ml);
         }
       }
     }

@@ -18,12 +18,12 @@ copy per tensor; the block table is published next to the token table.
 
 from __future__ import annotations
 
-from collections import OrderedDict
 from typing import Optional
 
 import torch
 
 from .paged_attention import PagedKVCacheManager, PagedReqTokensManager
+from .prefix_cache import NativePrefixCache
 
 
 class AttentionInfo:
@@ -49,7 +49,8 @@ class PagedKVExecutor:
 
     def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, num_pages: int,
                  max_requests: int, max_seq_len: int, page_size: int = 16,
-                 dtype: torch.dtype = torch.float16, device: str = "cuda:0"):
+                 dtype: torch.dtype = torch.float16, device: str = "cuda:0",
+                 prefix_cache_entries: int = 128, prefix_cache_block_entries: int = 4096):
         self.device = device
         self.page_size = page_size
         self.num_kv_heads = num_kv_heads
@@ -61,12 +62,12 @@ class PagedKVExecutor:
         self.atten_info = AttentionInfo()
         self.atten_info.kv_buffer = self.kv_mem_manager.gpu_kv_buffer
         self._paged_request_ids: tuple[int, ...] = ()
-        # exact-prompt cache: prompt -> (pages, tokens, first generated token); block cache:
-        # (parent fingerprint, block tokens) -> (page, tokens up to and including the block)
-        self._paged_prefix_cache: OrderedDict = OrderedDict()
-        self._paged_prefix_cache_max_entries = 128
-        self._paged_block_prefix_cache: OrderedDict = OrderedDict()
-        self._paged_block_prefix_cache_max_entries = 4096
+        # exact-prompt table: prompt -> (pages, tokens, first generated token); block table:
+        # (fingerprint of the blocks before, block tokens) -> (page, tokens up to and including
+        # the block); capacities as in the reference executor (model_executor.py:296,303)
+        self._paged_prefix_cache_max_entries = prefix_cache_entries
+        self._paged_block_prefix_cache_max_entries = prefix_cache_block_entries
+        self._prefix_cache = NativePrefixCache(page_size, prefix_cache_entries, prefix_cache_block_entries)
 
     # ------------------------------------------------------------------ helpers
     def _dev(self, values, dtype) -> torch.Tensor:
@@ -125,88 +126,71 @@ class PagedKVExecutor:
         self.release_paged_request_ids(self._paged_request_ids)
 
     # ------------------------------------------------------------------ prefix cache
-    @staticmethod
-    def _paged_block_key(parent_fingerprint, block_tokens):
-        return parent_fingerprint, tuple(int(t) for t in block_tokens)
+    # The tables themselves (exact prompts, blocks chained by parent fingerprint, both LRU) are
+    # native code (prefix_cache.NativePrefixCache); these methods keep the reference's names,
+    # arguments and return values (model_executor.py:547-683) and apply the reference changes the
+    # cache asks for to the page pool.
+    def _apply_ref_ops(self, ops) -> None:
+        pool = self.req_tokens_manager.page_mgr
+        for delta, pages in ops:
+            # a run may name a page twice (the prompt's reference and a block's); the pool's
+            # vectorised update counts an index once per call, so cut the run at every repeat
+            start, seen = 0, set()
+            for i, page in enumerate(pages.tolist() + [None]):
+                if page is None or page in seen:
+                    t = torch.from_numpy(pages[start:i])
+                    if delta > 0:
+                        pool.add_ref(t)
+                    else:
+                        pool.free(t)
+                    start, seen = i, set()
+                if page is not None:
+                    seen.add(page)
+
+    def _share(self, pages, num_tokens: int) -> Optional[int]:
+        return self.req_tokens_manager.reserve_shared_req(torch.from_numpy(pages), int(num_tokens))
 
     def share_paged_request_from_cache(self, prompt_tokens) -> Optional[tuple[int, int]]:
         """Exact full-prompt hit: ``(request_id, first generated token)`` or ``None``."""
-        key = tuple(int(t) for t in prompt_tokens)
-        cached = self._paged_prefix_cache.get(key)
-        if cached is None:
+        hit = self._prefix_cache.lookup_exact(prompt_tokens)
+        if hit is None:
             return None
-        self._paged_prefix_cache.move_to_end(key)
-        pages, num_tokens, first_token_id = cached
-        req_idx = self.req_tokens_manager.reserve_shared_req(pages, num_tokens)
-        if req_idx is None:
-            return None
-        return int(req_idx), int(first_token_id)
+        pages, num_tokens, first_token_id = hit
+        req_idx = self._share(pages, num_tokens)
+        return None if req_idx is None else (int(req_idx), first_token_id)
 
     def share_paged_prefix_from_cache(self, prompt_tokens) -> Optional[tuple[int, int, Optional[int]]]:
         """Longest cached page-aligned prefix: ``(request_id, matched_tokens, first_token_id)``;
         ``first_token_id`` is ``None`` for a partial hit (the caller prefills the suffix)."""
-        key = tuple(int(t) for t in prompt_tokens)
-        if not key:
+        n = len(prompt_tokens)
+        if n == 0:
             return None
-        exact = self._paged_prefix_cache.get(key)
-        if exact is not None:
-            self._paged_prefix_cache.move_to_end(key)
-            pages, num_tokens, first_token_id = exact
-            req_idx = self.req_tokens_manager.reserve_shared_req(pages, num_tokens)
-            if req_idx is None:
-                return None
-            return int(req_idx), len(key), int(first_token_id)
-        matched, matched_tokens, parent = [], 0, None
-        ps = int(self.page_size)
-        for start in range(0, len(key) - ps + 1, ps):
-            block_key = self._paged_block_key(parent, key[start: start + ps])
-            cached_block = self._paged_block_prefix_cache.get(block_key)
-            if cached_block is None:
-                break
-            self._paged_block_prefix_cache.move_to_end(block_key)
-            page_index, token_count = cached_block
-            matched.append(page_index.reshape(-1))
-            matched_tokens = int(token_count)
-            parent = hash(block_key)
-        if not matched or matched_tokens <= 0:
+        hit = self._prefix_cache.lookup_exact(prompt_tokens)
+        if hit is not None:
+            pages, num_tokens, first_token_id = hit
+            req_idx = self._share(pages, num_tokens)
+            return None if req_idx is None else (int(req_idx), n, first_token_id)
+        pages, matched_tokens = self._prefix_cache.lookup_blocks(prompt_tokens)
+        if pages.shape[0] == 0 or matched_tokens <= 0:
             return None
-        pages = torch.cat(matched).to(device="cpu", dtype=torch.long)
-        req_idx = self.req_tokens_manager.reserve_shared_req(pages, matched_tokens)
-        if req_idx is None:
-            return None
-        return int(req_idx), int(matched_tokens), None
-
-    def _store_paged_prompt_blocks(self, prompt_tokens: tuple[int, ...], page_indices) -> None:
-        ps = int(self.page_size)
-        parent = None
-        for block_index in range(len(prompt_tokens) // ps):
-            block_key = self._paged_block_key(parent, prompt_tokens[block_index * ps: (block_index + 1) * ps])
-            parent = hash(block_key)
-            if block_key in self._paged_block_prefix_cache:
-                self._paged_block_prefix_cache.move_to_end(block_key)
-                continue
-            page_index = page_indices[block_index: block_index + 1].clone()
-            self.req_tokens_manager.page_mgr.add_ref(page_index)      # the cache holds its own reference
-            self._paged_block_prefix_cache[block_key] = (page_index, (block_index + 1) * ps)
-            while len(self._paged_block_prefix_cache) > self._paged_block_prefix_cache_max_entries:
-                _, (old_page, _) = self._paged_block_prefix_cache.popitem(last=False)
-                self.req_tokens_manager.page_mgr.free(old_page)
+        req_idx = self._share(pages, matched_tokens)
+        return None if req_idx is None else (int(req_idx), matched_tokens, None)
 
     def store_paged_request_prefix(self, prompt_tokens, req_idx: int, first_token_id: int) -> None:
-        """Keep a finished prompt's pages alive for reuse (one extra reference per page)."""
-        if req_idx not in self.req_tokens_manager.req_page_table:
+        """Keep a finished prompt's pages alive for reuse: one reference per page for the whole
+        prompt, one more per full block that the block table did not know yet; entries evicted to
+        make room give theirs back."""
+        mgr = self.req_tokens_manager
+        if req_idx not in mgr.req_page_table:
             return
-        key = tuple(int(t) for t in prompt_tokens)
-        if key in self._paged_prefix_cache:
-            return
-        pages = self.req_tokens_manager.req_page_table[int(req_idx)]
-        self.req_tokens_manager.page_mgr.add_ref(pages)
-        self._paged_prefix_cache[key] = (pages.clone(), int(self.req_tokens_manager.req_token_count[int(req_idx)]),
-                                         int(first_token_id))
-        self._store_paged_prompt_blocks(key, pages)
-        while len(self._paged_prefix_cache) > self._paged_prefix_cache_max_entries:
-            _, (old_pages, _, _) = self._paged_prefix_cache.popitem(last=False)
-            self.req_tokens_manager.page_mgr.free(old_pages)
+        pages = mgr.req_page_table[int(req_idx)]
+        ops = self._prefix_cache.store(prompt_tokens, pages.numpy(), mgr.req_token_count[int(req_idx)],
+                                       first_token_id)
+        self._apply_ref_ops(ops)
+
+    def clear_paged_prefix_cache(self) -> None:
+        """Forget every cached prefix and drop the references the cache held."""
+        self._apply_ref_ops(self._prefix_cache.clear())
 
     # ------------------------------------------------------------------ batch activation
     def activate_paged_prefill_batch(self, request_ids: tuple[int, ...], prompt_length: int) -> None:

@@ -234,3 +234,96 @@ def host_script(paged, kveng) -> dict:
                    "rows": [[r.request_index, r.start, r.length, r.end] for r in pk.requests],
                    "total": pk.total_tokens, "batch": pk.batch_size}
     return log
+
+
+# Prefix-cache script: small capacities so that both tables evict; page_size 4.
+PREFIX_CACHE_SCRIPT = {
+    "page_size": 4, "num_pages": 40, "max_requests": 12, "max_seq_len": 32, "max_exact": 3, "max_block": 6,
+}
+
+
+def run_prefix_cache_script(ex, mgr, sizes) -> list:
+    """Drive an executor-like object ``ex`` (prefix-cache methods of the reference's ModelExecutor)
+    over request manager ``mgr`` through a fixed call sequence; after every call record the return
+    value, the table sizes and the page pool's observable state."""
+    pm = mgr.page_mgr
+    log = []
+
+    def snap(call, ret):
+        log.append({
+            "call": call, "ret": ret, "sizes": list(sizes()), "free": int(pm.num_free_pages),
+            "refcount": [int(x) for x in pm.page_refcount.tolist()],
+            "req_pages": {str(k): [int(x) for x in v.tolist()] for k, v in sorted(mgr.req_page_table.items())},
+            "req_tokens": {str(k): int(v) for k, v in sorted(mgr.req_token_count.items())},
+        })
+
+    def prompt(seed, n):   # deterministic token ids, distinct per seed, shared 8-token head for seeds < 10
+        head = [1000 + i for i in range(8)] if seed < 10 else [2000 + seed * 7 + i for i in range(8)]
+        return tuple((head + [seed * 100 + i for i in range(n)])[:n])
+
+    def new_request(tokens):
+        return mgr.reserve_req(len(tokens))
+
+    def norm(ret):
+        return None if ret is None else [None if x is None else int(x) for x in ret]
+
+    prompts = {
+        "a": prompt(1, 13), "b": prompt(2, 16), "c": prompt(3, 9), "d": prompt(11, 12), "e": prompt(12, 8),
+        "f": prompt(4, 20), "short": prompt(5, 3),
+    }
+    live = {}
+    # 1. misses on an empty cache
+    snap("share_prefix a (empty)", norm(ex.share_paged_prefix_from_cache(prompts["a"])))
+    snap("share_exact a (empty)", norm(ex.share_paged_request_from_cache(prompts["a"])))
+    snap("share_prefix () ", norm(ex.share_paged_prefix_from_cache(())))
+    # 2. store a and b (they share the first two blocks), then hit them
+    for name in ("a", "b"):
+        live[name] = new_request(prompts[name])
+        ex.store_paged_request_prefix(prompts[name], live[name], 500 + len(prompts[name]))
+        snap(f"store {name}", None)
+    ex.store_paged_request_prefix(prompts["a"], live["a"], 999)          # already stored: no change
+    snap("store a again", None)
+    ex.store_paged_request_prefix(prompts["c"], 11, 1)                    # unknown request id: ignored
+    snap("store unknown request", None)
+    r = ex.share_paged_request_from_cache(prompts["a"])
+    snap("share_exact a", norm(r))
+    live["a2"] = r[0]
+    r = ex.share_paged_prefix_from_cache(prompts["b"])
+    snap("share_prefix b (exact)", norm(r))
+    live["b2"] = r[0]
+    r = ex.share_paged_prefix_from_cache(prompts["c"])                    # partial: the shared head blocks
+    snap("share_prefix c (partial)", norm(r))
+    live["c_part"] = r[0]
+    snap("share_prefix short", norm(ex.share_paged_prefix_from_cache(prompts["short"])))
+    snap("share_prefix d (miss)", norm(ex.share_paged_prefix_from_cache(prompts["d"])))
+    # 3. more stores: the block table (6) and then the exact table (3) evict
+    for name in ("d", "e", "f"):
+        live[name] = new_request(prompts[name])
+        ex.store_paged_request_prefix(prompts[name], live[name], 600 + len(prompts[name]))
+        snap(f"store {name}", None)
+    snap("share_exact a (evicted?)", norm(ex.share_paged_request_from_cache(prompts["a"])))
+    r = ex.share_paged_prefix_from_cache(prompts["f"])
+    snap("share_prefix f", norm(r))
+    live["f2"] = r[0]
+    r = ex.share_paged_prefix_from_cache(prompts["a"])
+    snap("share_prefix a (after evictions)", norm(r))
+    if r is not None:
+        live["a3"] = r[0]
+    # 4. release every request: what stays referenced is what the caches hold
+    for name in sorted(live):
+        mgr.free_req(live[name])
+    snap("all requests released", None)
+    # 5. a hit with no free request row left
+    taken = []
+    while True:
+        rid = mgr.reserve_req(1)
+        if rid is None:
+            break
+        taken.append(rid)
+    snap("rows exhausted", len(taken))
+    snap("share_exact f (no row)", norm(ex.share_paged_request_from_cache(prompts["f"])))
+    snap("share_prefix e (no row)", norm(ex.share_paged_prefix_from_cache(prompts["e"])))
+    for rid in taken:
+        mgr.free_req(rid)
+    snap("rows returned", None)
+    return log
