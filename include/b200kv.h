@@ -253,19 +253,24 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h,
  * followed by b200kv_paged_decode(...): update_kv_buffer then flash_decoding in
  * Attention.token_forward (lite_llama/models/qwen3.py:62-74).  The pool rows
  * are written bit-exactly.
- *   new_kv     fp16 [batch, 2*kv_heads, head_dim] (K heads first), token stride
- *              new_kv_tok_stride: the step's new K/V row of every sequence
+ *   new_k, new_v  fp16 [batch, kv_heads, head_dim] each, token strides
+ *              new_k_tok_stride / new_v_tok_stride: the step's new K and V row of
+ *              every sequence.  For one combined [batch, 2*kv_heads, head_dim]
+ *              tensor (K heads first) pass new_v = new_k + kv_heads*head_dim and
+ *              the same stride twice
  *   slots      int32 [batch] slot_mapping; slots[b] must be the slot of the LAST
  *              token of sequence b, i.e. position seq_lens[b] - 1 of its table
  *              row (seq_lens already counts the new token).  A slot outside the
  *              pool is skipped, one that is not that position is still written;
  *              both set B200KV_DEV_BAD_SLOT
  *   k_base, v_base  as for b200kv_paged_decode, but written to
- * new_kv and slots may come from the kernel launched immediately before; the
+ * new_k / new_v and slots may come from the kernel launched immediately before; the
  * rule for seq_lens / row_ids / table stands.  Sequences of length 0 append
  * nothing.
  */
-int b200kv_append_paged_decode(const void* new_kv, int64_t new_kv_tok_stride, const int32_t* slots,
+int b200kv_append_paged_decode(const void* new_k, const void* new_v,
+                               int64_t new_k_tok_stride, int64_t new_v_tok_stride,
+                               const int32_t* slots,
                                const void* q, int64_t q_stride_b, int64_t q_stride_h,
                                void* k_base, void* v_base,
                                int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,

@@ -67,7 +67,7 @@ _SIGNATURES = {
     ),
     "b200kv_append_paged_decode": (
         c_int,
-        [c_void_p, c_int64, c_void_p,            # new_kv, token stride, slots
+        [c_void_p, c_void_p, c_int64, c_int64, c_void_p,   # new K, new V, their token strides, slots
          c_void_p, c_int64, c_int64,
          c_void_p, c_void_p, c_int64, c_int64, c_int64,
          c_void_p, c_int64, c_int, c_int, c_int64,

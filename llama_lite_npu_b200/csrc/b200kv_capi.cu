@@ -213,7 +213,8 @@ int b200kv_paged_decode(const void* q, int64_t q_stride_b, int64_t q_stride_h, c
   return b200kv::paged_decode(a, static_cast<cudaStream_t>(stream));
 }
 
-int b200kv_append_paged_decode(const void* new_kv, int64_t new_kv_tok_stride, const int32_t* slots,
+int b200kv_append_paged_decode(const void* new_k, const void* new_v, int64_t new_k_tok_stride,
+                               int64_t new_v_tok_stride, const int32_t* slots,
                                const void* q, int64_t q_stride_b, int64_t q_stride_h, void* k_base,
                                void* v_base, int64_t kv_tok_stride, int64_t kv_head_stride,
                                int64_t pool_tokens, const int32_t* table, int64_t table_row_stride,
@@ -223,14 +224,16 @@ int b200kv_append_paged_decode(const void* new_kv, int64_t new_kv_tok_stride, co
                                int64_t max_seq_len, void* workspace, size_t workspace_bytes, void* out,
                                int64_t out_stride_b, int64_t out_stride_h, int flags, int32_t* status,
                                void* stream) {
-  if (batch > 0 && (new_kv == nullptr || slots == nullptr)) return B200KV_EINVAL;
+  if (batch > 0 && (new_k == nullptr || new_v == nullptr || slots == nullptr)) return B200KV_EINVAL;
   b200kv::DecodeArgs a = decode_args(q, q_stride_b, q_stride_h, k_base, v_base, kv_tok_stride, kv_head_stride,
                                      pool_tokens, table, table_row_stride, table_kind, table_rows, table_cols,
                                      row_ids, seq_lens, seq_lens_i64, batch, q_heads, kv_heads, head_dim,
                                      page_size, scale, max_seq_len, out, out_stride_b, out_stride_h, flags,
                                      status);
-  a.new_kv = new_kv;
-  a.new_kv_tok_stride = new_kv_tok_stride;
+  a.new_k = new_k;
+  a.new_v = new_v;
+  a.new_k_tok_stride = new_k_tok_stride;
+  a.new_v_tok_stride = new_v_tok_stride;
   a.slots = slots;
   a.workspace = workspace;
   a.workspace_bytes = workspace_bytes;

@@ -77,8 +77,9 @@ struct DecodeArgs {
   const int32_t* row_ids;
   const void* seq_lens;
   int seq_lens_i64;
-  const void* new_kv;          // fused append: nullptr = none
-  int64_t new_kv_tok_stride;
+  const void* new_k;           // fused append: nullptr = none
+  const void* new_v;
+  int64_t new_k_tok_stride, new_v_tok_stride;
   const int32_t* slots;
   int batch, q_heads, kv_heads, head_dim, page_size;
   float scale;

@@ -74,6 +74,11 @@ constexpr int kMinPagesPerTeam = 4;   // a team is not worth launching for fewer
 // with more sequence boundaries get fewer pages; a team boundary that falls inside a sequence's
 // extra units snaps to the start of that sequence.
 constexpr int kDefaultPieceCost = 8;
+// Pages per CTA (by the host's length bound) below which the cut is tuned for short ranges;
+// measured on KV-head shards of 32 sequences of 1-4 k tokens (1, 2, 4, 8 KV heads per GPU).
+constexpr int kMediumRangePages = 128;
+constexpr int kShortRangePages = 64;
+constexpr int kShortRangePieceCost = 16;
 // The first bytes of the workspace hold one arrival counter per (sequence, KV head).
 constexpr size_t kCounterBytes = B200KV_DECODE_COUNTER_BYTES;
 constexpr int64_t kMaxCounters = static_cast<int64_t>(kCounterBytes / sizeof(unsigned));
@@ -96,9 +101,10 @@ struct DecodeParams {
   int64_t max_seq_len;
   int nteams;
   int piece_cost;
-  // fused KV append (new_kv == nullptr: none): pool[slots[b]] = new_kv[b] for this CTA's head
-  const __half* new_kv;       // [batch][2*kv_heads][128], K heads first
-  int64_t new_kv_tok_stride;
+  // fused KV append (new_k == nullptr: none): pool[slots[b]] = (new_k[b], new_v[b]) for this CTA's head
+  const __half* new_k;        // [batch][kv_heads][128], token stride new_k_tok_stride
+  const __half* new_v;
+  int64_t new_k_tok_stride, new_v_tok_stride;
   const int32_t* slots;
   float* part_o;        // [nslots][kv_heads][ROWS][128]
   float* part_lse;      // [nslots][kv_heads][ROWS]
@@ -228,8 +234,9 @@ struct Fetch {
 // only read after the dependency wait.
 __device__ __forceinline__ void load_new_row(const DecodeParams& p, Fetch& f, int head, int lane) {
   f.app_slot = __ldg(p.slots + f.app_b);
-  const __half* src = p.new_kv + static_cast<int64_t>(f.app_b) * p.new_kv_tok_stride +
-                      static_cast<int64_t>((lane < 16 ? 0 : p.kv_heads) + head) * kD + (lane & 15) * 8;
+  const __half* src = (lane < 16 ? p.new_k + static_cast<int64_t>(f.app_b) * p.new_k_tok_stride
+                                 : p.new_v + static_cast<int64_t>(f.app_b) * p.new_v_tok_stride) +
+                      static_cast<int64_t>(head) * kD + (lane & 15) * 8;
   const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));
   f.app_row0 = v.x;
   f.app_row1 = v.y;
@@ -259,7 +266,7 @@ __device__ __forceinline__ void fetch_next(const DecodeParams& p, Walker& w, Fet
       f.id[i] = __ldg(rowp + (p.table_kind == B200KV_TABLE_BLOCK ? lp : lp * kPS));
     }
   }
-  if (p.new_kv != nullptr && t.page0 + t.npages == t.np) {
+  if (p.new_k != nullptr && t.page0 + t.npages == t.np) {
     f.app_b = t.b;
     f.app_off = (t.len - 1) & (kPS - 1);
     if (after_wait) load_new_row(p, f, head, lane);
@@ -303,7 +310,8 @@ __device__ __forceinline__ void consumer_bar() {
 //      and the row maxima are reduced with shuffles and one pass through shared memory;
 //   B. the same threads turn their entries into weights 2^(lse - M) in place and reduce the row sums;
 //   C. thread = output column: the partial outputs are loaded kMergeBatch pieces at a time, every
-//      load of a batch issued before any arithmetic, and weighted with the shared-memory weights.
+//      load of a batch issued before any arithmetic (the first batch before step A even), and
+//      weighted with the shared-memory weights.
 // `wbuf` (npieces * ROWS floats) and `red` (2 * 4 * ROWS floats) are shared-memory scratch that
 // nobody else uses between the surrounding consumer barriers.
 constexpr int kMergeBatch = 6;
@@ -315,6 +323,18 @@ __device__ __forceinline__ void merge_pieces(const DecodeParams& p, int b, int h
   const int lane = tid & 31;
   const int warp = tid >> 5;
   auto slot_of = [&](int pc) { return (static_cast<int64_t>(t_first + pc) + b) * p.kv_heads + head; };
+  auto load_batch = [&](float (&ov)[kMergeBatch][8], int r0, int p0) {
+#pragma unroll
+    for (int j = 0; j < kMergeBatch; ++j) {
+      const int64_t slot = slot_of(min(p0 + j, npieces - 1));
+#pragma unroll
+      for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
+    }
+  };
+  // The first batch of partial outputs needs no weights to be requested: its loads are issued
+  // now and are in flight under steps A and B.
+  float first[kMergeBatch][8];
+  load_batch(first, 0, 0);
   // ---- A: log-sum-exp values -> shared memory, row maxima --------------------------------------
   float m = -INFINITY;
   for (int j = tid / ROWS; j < npieces; j += kPerSweep) {
@@ -340,29 +360,28 @@ __device__ __forceinline__ void merge_pieces(const DecodeParams& p, int b, int h
   if (lane < ROWS) red_sum[warp * ROWS + lane] = sum;
   consumer_bar();
   // ---- C: weighted sum of the partial outputs, thread = column -----------------------------------
+  auto add_batch = [&](float (&acc)[8], const float (&ov)[kMergeBatch][8], int r0, int p0) {
+#pragma unroll
+    for (int j = 0; j < kMergeBatch; ++j) {
+      if (p0 + j < npieces) {
+        const float4 w0 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0);
+        const float4 w1 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0 + 4);
+        acc[0] += w0.x * ov[j][0]; acc[1] += w0.y * ov[j][1]; acc[2] += w0.z * ov[j][2]; acc[3] += w0.w * ov[j][3];
+        acc[4] += w1.x * ov[j][4]; acc[5] += w1.y * ov[j][5]; acc[6] += w1.z * ov[j][6]; acc[7] += w1.w * ov[j][7];
+      }
+    }
+  };
 #pragma unroll 1
   for (int r0 = 0; r0 < ROWS && r0 < p.group; r0 += 8) {
     float acc[8];
 #pragma unroll
     for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+    if (r0 == 0) add_batch(acc, first, 0, 0);
 #pragma unroll 1
-    for (int p0 = 0; p0 < npieces; p0 += kMergeBatch) {
+    for (int p0 = (r0 == 0 ? kMergeBatch : 0); p0 < npieces; p0 += kMergeBatch) {
       float ov[kMergeBatch][8];
-#pragma unroll
-      for (int j = 0; j < kMergeBatch; ++j) {
-        const int64_t slot = slot_of(min(p0 + j, npieces - 1));
-#pragma unroll
-        for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
-      }
-#pragma unroll
-      for (int j = 0; j < kMergeBatch; ++j) {
-        if (p0 + j < npieces) {
-          const float4 w0 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0);
-          const float4 w1 = *reinterpret_cast<const float4*>(wbuf + (p0 + j) * ROWS + r0 + 4);
-          acc[0] += w0.x * ov[j][0]; acc[1] += w0.y * ov[j][1]; acc[2] += w0.z * ov[j][2]; acc[3] += w0.w * ov[j][3];
-          acc[4] += w1.x * ov[j][4]; acc[5] += w1.y * ov[j][5]; acc[6] += w1.z * ov[j][6]; acc[7] += w1.w * ov[j][7];
-        }
-      }
+      load_batch(ov, r0, p0);
+      add_batch(acc, ov, r0, p0);
     }
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
@@ -976,7 +995,8 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   if (a.row_ids == nullptr && a.batch > a.table_rows) return B200KV_EINVAL;
   const int64_t width_tokens = a.table_cols * (a.table_kind == B200KV_TABLE_BLOCK ? kPS : 1);
   if (a.max_seq_len > width_tokens) return B200KV_EINVAL;
-  if ((a.new_kv == nullptr) != (a.slots == nullptr)) return B200KV_EINVAL;
+  if ((a.new_k == nullptr) != (a.slots == nullptr) || (a.new_k == nullptr) != (a.new_v == nullptr))
+    return B200KV_EINVAL;
   if (a.flags & ~B200KV_DECODE_SERIALIZED) return B200KV_EINVAL;
   auto mis = [](const void* ptr, uintptr_t al) { return (reinterpret_cast<uintptr_t>(ptr) & (al - 1)) != 0; };
   if (mis(a.k_base, 16) || mis(a.v_base, 16) || mis(a.q, 4) || mis(a.out, 8) || mis(a.workspace, 16))
@@ -984,9 +1004,12 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   if (a.kv_tok_stride % 8 != 0 || a.kv_head_stride % 8 != 0) return B200KV_EALIGN;
   if (a.q_stride_b % 2 != 0 || a.q_stride_h % 2 != 0) return B200KV_EALIGN;
   if (a.out_stride_b % 4 != 0 || a.out_stride_h % 4 != 0) return B200KV_EALIGN;
-  if (a.new_kv != nullptr) {
-    if (mis(a.new_kv, 16) || a.new_kv_tok_stride % 8 != 0) return B200KV_EALIGN;
-    if (a.new_kv_tok_stride < static_cast<int64_t>(2) * a.kv_heads * kD) return B200KV_EINVAL;
+  if (a.new_k != nullptr) {
+    if (mis(a.new_k, 16) || mis(a.new_v, 16) || a.new_k_tok_stride % 8 != 0 || a.new_v_tok_stride % 8 != 0)
+      return B200KV_EALIGN;
+    if (a.new_k_tok_stride < static_cast<int64_t>(a.kv_heads) * kD ||
+        a.new_v_tok_stride < static_cast<int64_t>(a.kv_heads) * kD)
+      return B200KV_EINVAL;
   }
   const size_t need = decode_workspace_bytes(a.batch, a.q_heads, a.kv_heads, a.head_dim);
   if (need == 0) return B200KV_ECUDA;
@@ -998,9 +1021,23 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   // Do not launch more teams than the page bound can feed.
   const int64_t pages_bound = static_cast<int64_t>(a.batch) * ((a.max_seq_len + kPS - 1) / kPS);
   int64_t teams = pages_bound / kMinPagesPerTeam;
-  if (g_option_teams > 0 && teams > g_option_teams) teams = g_option_teams;
   if (teams > teams_cap) teams = teams_cap;
+  int piece_cost = kDefaultPieceCost;
+  if (teams == teams_cap && pages_bound < static_cast<int64_t>(kMediumRangePages) * teams_cap) {
+    // Ranges of a few dozen pages per CTA (KV-head shards of a modest batch): most pieces are
+    // partial ones, whose ends cost more (publish, count, maybe merge), so they weigh more
+    // against the pages when the line is cut.
+    piece_cost = kShortRangePieceCost;
+    if (pages_bound < static_cast<int64_t>(kShortRangePages) * teams_cap) {
+      // Shorter still: the launch is latency-bound rather than bandwidth-bound.  Seven eighths of
+      // the CTA slots stream as fast, leave slots free for the next launch's CTAs to do their
+      // planning under this launch's tail, and cut every sequence in fewer pieces.
+      teams = (7 * static_cast<int64_t>(teams_cap)) / 8;
+    }
+  }
+  if (g_option_teams > 0 && teams > g_option_teams) teams = g_option_teams;
   if (teams < 1) teams = 1;
+  if (g_option_piece_cost > 0) piece_cost = g_option_piece_cost;
 
   DecodeParams p{};
   p.q = static_cast<const __half*>(a.q);
@@ -1025,9 +1062,11 @@ int paged_decode(const DecodeArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.max_seq_len = a.max_seq_len;
   p.nteams = static_cast<int>(teams);
-  p.piece_cost = g_option_piece_cost > 0 ? g_option_piece_cost : kDefaultPieceCost;
-  p.new_kv = static_cast<const __half*>(a.new_kv);
-  p.new_kv_tok_stride = a.new_kv_tok_stride;
+  p.piece_cost = piece_cost;
+  p.new_k = static_cast<const __half*>(a.new_k);
+  p.new_v = static_cast<const __half*>(a.new_v);
+  p.new_k_tok_stride = a.new_k_tok_stride;
+  p.new_v_tok_stride = a.new_v_tok_stride;
   p.slots = a.slots;
   const size_t nslots = static_cast<size_t>(teams_cap) + static_cast<size_t>(a.batch);
   uint8_t* ws = static_cast<uint8_t*>(a.workspace);

@@ -42,6 +42,30 @@ class AttentionInfo:
         self.chunk_context_len = None
         self.chunk_q_seq_len = None
         self.max_actual_q_seq_len = None
+        self.page_size = 16
+        # the device half of a staged decode step that has not run yet (see PendingAdvance)
+        self.pending_advance = None
+
+
+class PendingAdvance:
+    """The device half of a staged decode step: every sequence of the active batch grows by one
+    token — lengths + 1, the new tokens' slots, their token-table entries — in one small kernel on
+    the tensors of the ``AttentionInfo`` it is run on.  The host half (page allocation, mirrors,
+    the new block-table entry of a sequence that crossed a page boundary) has already happened
+    when this object exists.  A graph runner records ``run`` as the first node of the step's
+    graph; everybody else calls it once before the layer steps."""
+
+    def __init__(self, executor: "PagedKVExecutor"):
+        self._ex = executor
+
+    def run(self, info) -> None:
+        from . import kernels
+
+        ex = self._ex
+        kernels.advance_decode_metadata(
+            info.b_seq_len, info.cur_select_index, info.b_req_block_table, ex.page_size,
+            ex.kv_mem_manager.num_pages, b_req_idx=info.b_req_idx,
+            page_counts=ex.req_tokens_manager.page_counts, b_req_tokens_table=info.b_req_tokens_table)
 
 
 class PagedKVExecutor:
@@ -60,6 +84,7 @@ class PagedKVExecutor:
         self.req_tokens_manager = PagedReqTokensManager(max_requests, max_seq_len,
                                                         self.kv_mem_manager, device)
         self.atten_info = AttentionInfo()
+        self.atten_info.page_size = page_size
         self.atten_info.kv_buffer = self.kv_mem_manager.gpu_kv_buffer
         self._paged_request_ids: tuple[int, ...] = ()
         # exact-prompt table: prompt -> (pages, tokens, first generated token); block table:
@@ -299,19 +324,22 @@ class PagedKVExecutor:
                     f"max_seq_len={mgr.max_seq_len}, free_pages={mgr.page_mgr.num_free_pages}")
         self.activate_paged_decode_batch(request_ids)
 
-    def extend_paged_requests_on_device(self, request_ids: tuple[int, ...]) -> None:
-        """``extend_paged_requests`` with the per-step metadata produced on the device.
+    def stage_paged_decode_step(self, request_ids: tuple[int, ...]) -> None:
+        """Host half of one decode step of the active batch; the device half stays pending.
 
-        When the batch is the one that is already active, its ``b_seq_len`` / ``cur_select_index``
-        tensors are advanced in place by one small kernel: nothing is copied from the host unless a
-        sequence crossed a page boundary (then only the new block-table entry is).  The tensors
-        keep their addresses, so a captured decode step can be replayed as is.  Any other batch
-        goes through the host path once, which also makes it the active one."""
-        if tuple(request_ids) != self._paged_request_ids or self.atten_info.b_seq_len is None:
+        When the batch is the one that is already active: pages are allocated for sequences that
+        cross a page boundary (only then does anything cross PCIe: the new block-table entry), the
+        host mirrors advance, and ``atten_info.pending_advance`` is set to the kernel launch that
+        will advance ``b_seq_len`` / ``cur_select_index`` / the token table in place.  The tensors
+        keep their addresses, so a graph that holds that launch and the layer steps can be
+        replayed as is (``cuda_graph.CudaGraphRunner`` does exactly this).  Any other batch goes
+        through the host path once (nothing stays pending), which also makes it the active one."""
+        info = self.atten_info
+        if info.pending_advance is not None:
+            raise RuntimeError("the previous decode step was staged but its device half never ran")
+        if tuple(request_ids) != self._paged_request_ids or info.b_seq_len is None:
             self.extend_paged_requests(request_ids)
             return
-        from . import kernels
-
         mgr = self.req_tokens_manager
         failed = mgr.extend_batch_for_device(request_ids)
         if failed is not None:
@@ -319,13 +347,18 @@ class PagedKVExecutor:
                 "Paged KV allocation failed for request "
                 f"{failed}: current_tokens={mgr.req_token_count.get(failed, 'unknown')}, "
                 f"max_seq_len={mgr.max_seq_len}, free_pages={mgr.page_mgr.num_free_pages}")
-        info = self.atten_info
         self._publish_tables()                                   # flushes a new page entry, if any
-        kernels.advance_decode_metadata(
-            info.b_seq_len, info.cur_select_index, info.b_req_block_table, self.page_size,
-            self.kv_mem_manager.num_pages, b_req_idx=info.b_req_idx, page_counts=mgr.page_counts,
-            b_req_tokens_table=info.b_req_tokens_table)
         info.max_actual_seq_len += 1
+        info.pending_advance = PendingAdvance(self)
+
+    def extend_paged_requests_on_device(self, request_ids: tuple[int, ...]) -> None:
+        """``extend_paged_requests`` with the per-step metadata produced on the device:
+        ``stage_paged_decode_step`` followed at once by its device half."""
+        self.stage_paged_decode_step(request_ids)
+        info = self.atten_info
+        if info.pending_advance is not None:
+            info.pending_advance.run(info)
+            info.pending_advance = None
 
     # ------------------------------------------------------------------ attention call sequences
     def context_forward(self, xq, xk, xv, layer_index: int, qk_scale: float) -> torch.Tensor:
@@ -350,12 +383,13 @@ class PagedKVExecutor:
         selected by ``b_req_idx``, so batches with gaps or reordered request ids are correct."""
         from . import kernels
 
-        info, kh = self.atten_info, self.num_kv_heads
-        pool = info.kv_buffer[layer_index]
-        kernels.update_kv_buffer_split(xk, xv, info.cur_select_index, pool)
-        return kernels.flash_decoding(
-            xq, pool[:, :kh, :], pool[:, kh:, :], qk_scale, info.b_req_block_table, info.b_seq_len,
-            info.max_actual_seq_len, b_req_idx=info.b_req_idx, table_kind="block")
+        info = self.atten_info
+        # one launch: append + decode.  The first layer's launch may directly follow the kernel or
+        # copy that produced the step's lengths, so it gives up its overlap with its predecessor.
+        return kernels.append_flash_decoding_split(
+            xk, xv, info.cur_select_index, info.kv_buffer[layer_index], xq, qk_scale, info.b_req_block_table,
+            info.b_seq_len, info.max_actual_seq_len, b_req_idx=info.b_req_idx, table_kind="block",
+            metadata_fresh=(layer_index == 0))
 
     # ------------------------------------------------------------------ fused prologue variants
     def fused_token_forward(self, xq, xkv, q_norm_weight, k_norm_weight, eps: float, cos, sin,

@@ -9,9 +9,12 @@ CUDA stream.  PyTorch is used for memory (outputs, the split-KV workspace) and
 streams only.  There is no CPU path: tensors must live on a CUDA device and the
 shared library must be present.
 
-Debugging aid: with the environment variable ``B200KV_DEBUG=1`` every call is
-followed by a device synchronisation and a check of the device status word
-(out-of-range slots / page ids / lengths), raising ``RuntimeError``.
+Debugging aid: with the environment variable ``B200KV_DEBUG=1`` (or ``set_debug(True)``) every
+call first validates its index tensors on the host — slots inside the pool, no two tokens of one
+append aimed at the same slot with different payloads, lengths within the stated maximum, table
+rows inside the table — raising ``ValueError`` before anything is launched, and is followed by a
+device synchronisation and a check of the device status word, raising ``RuntimeError``.  Both
+cost a device round trip per call; neither runs otherwise.
 """
 
 from __future__ import annotations
@@ -76,6 +79,47 @@ def check_status(device_index: Optional[int] = None) -> None:
 def _after_call(device_index: int) -> None:
     if _DEBUG:
         check_status(device_index)
+
+
+def set_debug(enabled: bool) -> None:
+    """Switch the debug mode described in the module docstring on or off."""
+    global _DEBUG
+    _DEBUG = bool(enabled)
+
+
+def _debug_check_append(values: torch.Tensor, slots: torch.Tensor, pool_tokens: int) -> None:
+    """Host-side look at a slot_mapping before the append is launched (debug mode only).
+
+    Slots must lie inside the pool.  Two tokens may name the same slot only with identical
+    payloads (an exact-prompt prefix hit shares its partially filled last page and both owners
+    append the same row, ``lite_llama/executor/model_executor.py:547-568``); different payloads
+    would make the result depend on which write lands last."""
+    n = slots.shape[0]
+    if n == 0:
+        return
+    s = slots.long()
+    bad = (s < 0) | (s >= pool_tokens)
+    if bool(bad.any()):
+        i = int(bad.nonzero()[0])
+        raise ValueError(f"slot_mapping[{i}] = {int(s[i])} is outside the pool of {pool_tokens} token slots")
+    order = torch.argsort(s, stable=True)
+    same = s[order][1:] == s[order][:-1]
+    if bool(same.any()):
+        a, b = order[:-1][same], order[1:][same]
+        rows = values[:n].reshape(n, -1)
+        differ = (rows[a] != rows[b]).any(dim=1)
+        if bool(differ.any()):
+            j = int(differ.nonzero()[0])
+            raise ValueError(f"tokens {int(a[j])} and {int(b[j])} are both appended to slot {int(s[a[j]])} "
+                             "with different K/V rows")
+
+
+def _debug_check_lengths(lens: torch.Tensor, max_len: int, rows: Optional[torch.Tensor], table_rows: int,
+                         what: str) -> None:
+    if lens.numel() and (int(lens.min()) < 0 or int(lens.max()) > max_len):
+        raise ValueError(f"{what}: a length lies outside [0, {max_len}]")
+    if rows is not None and rows.numel() and (int(rows.min()) < 0 or int(rows.max()) >= table_rows):
+        raise ValueError(f"{what}: a request id lies outside the table's {table_rows} rows")
 
 
 def _stream(device_index: int) -> int:
@@ -177,6 +221,8 @@ def update_kv_buffer(KV_Values: torch.Tensor, Select_Index: torch.Tensor, KV_Buf
              "KV_Buffer must be contiguous inside a token")
     if not Select_Index.is_contiguous():
         Select_Index = Select_Index.contiguous()
+    if _DEBUG:
+        _debug_check_append(KV_Values, Select_Index, KV_Buffer.shape[0])
     with _on_device(dev):
         rc = _lib.lib().b200kv_kv_append(
             KV_Values.data_ptr(), n, KV_Values.stride(0), Select_Index.data_ptr(),
@@ -210,6 +256,8 @@ def update_kv_buffer_split(xk: torch.Tensor, xv: torch.Tensor, Select_Index: tor
         return
     if not Select_Index.is_contiguous():
         Select_Index = Select_Index.contiguous()
+    if _DEBUG:
+        _debug_check_append(torch.cat([xk[:n], xv[:n]], dim=1), Select_Index, KV_Buffer.shape[0])
     with _on_device(dev):
         rc = _lib.lib().b200kv_kv_append_split(
             xk.data_ptr(), xv.data_ptr(), n, xk.stride(0), xv.stride(0), Select_Index.data_ptr(),
@@ -353,8 +401,10 @@ def fused_qk_norm_rope_append(xq: torch.Tensor, xkv: torch.Tensor, q_norm_weight
     return out
 
 
-def _decode_call(new_kv, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, max_actual_seq_len,
+def _decode_call(new_rows, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, max_actual_seq_len,
                  b_req_idx, table_kind, page_size, out, metadata_fresh):
+    """Shared body of the decode operators; ``new_rows`` is ``None`` or ``(k_ptr, v_ptr, k_token_stride,
+    v_token_stride)`` of the step's new K/V rows for the fused append."""
     dev = _device_index(q)
     _require(q.dtype == torch.float16 and q.dim() == 3, "q must be float16 [batch, heads, head_dim]")
     assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
@@ -387,11 +437,13 @@ def _decode_call(new_kv, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, m
                  "out must match q")
     if batch == 0:
         return out
+    if _DEBUG:
+        _debug_check_lengths(b_seq_len, max_len, b_req_idx, tbl_rows, "decode")
     ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
     flags = DECODE_SERIALIZED if metadata_fresh else 0
     lib = _lib.lib()
     with _on_device(dev):
-        if new_kv is None:
+        if new_rows is None:
             rc = lib.b200kv_paged_decode(
                 q.data_ptr(), q_sb, q_sh,
                 k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
@@ -402,7 +454,7 @@ def _decode_call(new_kv, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, m
             )
         else:
             rc = lib.b200kv_append_paged_decode(
-                new_kv.data_ptr(), new_kv.stride(0), slots.data_ptr(),
+                new_rows[0], new_rows[1], new_rows[2], new_rows[3], slots.data_ptr(),
                 q.data_ptr(), q_sb, q_sh,
                 k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
                 tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr, lens_ptr, lens_i64,
@@ -483,9 +535,46 @@ def append_flash_decoding(
              and Select_Index.device == KV_Buffer.device, "Select_Index must be contiguous int32 [batch]")
     _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d, "KV_Buffer must be contiguous inside a token")
     kvh = rows // 2
-    return _decode_call(KV_Values, Select_Index, q, KV_Buffer[:, :kvh], KV_Buffer[:, kvh:], qk_scale,
-                        b_req_tokens_table, b_seq_len, max_actual_seq_len, b_req_idx, table_kind,
-                        page_size, out, metadata_fresh)
+    k_ptr, stride = KV_Values.data_ptr(), KV_Values.stride(0)
+    return _decode_call((k_ptr, k_ptr + kvh * d * 2, stride, stride), Select_Index, q, KV_Buffer[:, :kvh],
+                        KV_Buffer[:, kvh:], qk_scale, b_req_tokens_table, b_seq_len, max_actual_seq_len,
+                        b_req_idx, table_kind, page_size, out, metadata_fresh)
+
+
+def append_flash_decoding_split(
+    xk: torch.Tensor,
+    xv: torch.Tensor,
+    Select_Index: torch.Tensor,
+    KV_Buffer: torch.Tensor,
+    q: torch.Tensor,
+    qk_scale: float,
+    b_req_tokens_table: torch.Tensor,
+    b_seq_len: torch.Tensor,
+    max_actual_seq_len: int,
+    *,
+    b_req_idx: Optional[torch.Tensor] = None,
+    table_kind: str = "token",
+    page_size: int = 16,
+    out: Optional[torch.Tensor] = None,
+    metadata_fresh: bool = False,
+) -> torch.Tensor:
+    """:func:`append_flash_decoding` with the new K and V rows given separately
+    (``[batch, kv_heads, head_dim]`` each), i.e. without ``torch.cat([xk, xv], dim=-2)``
+    (``lite_llama/models/qwen3.py:62``)."""
+    _require(KV_Buffer.dim() == 3 and KV_Buffer.dtype == torch.float16 and KV_Buffer.shape[1] % 2 == 0,
+             "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
+    kvh, d = KV_Buffer.shape[1] // 2, KV_Buffer.shape[2]
+    batch = q.shape[0]
+    for t, name in ((xk, "xk"), (xv, "xv")):
+        _require(t.dtype == torch.float16 and t.shape == (batch, kvh, d) and t.stride(2) == 1 and t.stride(1) == d
+                 and t.device == KV_Buffer.device,
+                 f"{name} must be float16 [batch, kv_heads, head_dim] on the pool's device, contiguous inside a token")
+    _require(Select_Index.dtype == torch.int32 and Select_Index.shape == (batch,) and Select_Index.is_contiguous()
+             and Select_Index.device == KV_Buffer.device, "Select_Index must be contiguous int32 [batch]")
+    _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d, "KV_Buffer must be contiguous inside a token")
+    return _decode_call((xk.data_ptr(), xv.data_ptr(), xk.stride(0), xv.stride(0)), Select_Index, q,
+                        KV_Buffer[:, :kvh], KV_Buffer[:, kvh:], qk_scale, b_req_tokens_table, b_seq_len,
+                        max_actual_seq_len, b_req_idx, table_kind, page_size, out, metadata_fresh)
 
 
 def set_decode_option(option: int, value: int) -> None:
@@ -556,6 +645,9 @@ def paged_chunk_flash_attention(
              "context_lens and q_seq_lens must share dtype and shape")
     ctx_ptr, lens_i64 = _lens_arg(context_lens, "context_lens")
     qlen_ptr, _ = _lens_arg(q_seq_lens, "q_seq_lens")
+    if _DEBUG:
+        width = tbl.shape[1] * (page_size if kind == TABLE_BLOCK else 1)
+        _debug_check_lengths(context_lens + q_seq_lens, width, req_ids, tbl.shape[0], "paged prefill")
     return _prefill_call(q, k_cache, v_cache, sm_scale, tbl.data_ptr(), tbl.stride(0), kind,
                          tbl.shape[0], tbl.shape[1], req_ids.data_ptr(), q_start_loc, ctx_ptr, qlen_ptr,
                          lens_i64, batch, max_q_len, page_size)
@@ -593,9 +685,11 @@ __all__ = [
     "update_kv_buffer_split",
     "flash_decoding",
     "append_flash_decoding",
+    "append_flash_decoding_split",
     "paged_chunk_flash_attention",
     "flash_attention2_no_pad",
     "check_status",
+    "set_debug",
     "status_tensor",
     "decode_workspace",
 ]

@@ -33,3 +33,10 @@ def built_lib():
 
     build_library()
     return _lib.lib()
+
+
+@pytest.fixture(scope="session")
+def golden_signatures():
+    import json
+
+    return json.loads((ROOT / "tests" / "golden" / "host_golden.json").read_text())["signatures"]

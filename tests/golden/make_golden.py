@@ -18,6 +18,7 @@ from __future__ import annotations
 import argparse
 import hashlib
 import importlib.util
+import inspect
 import json
 import math
 import sys
@@ -113,7 +114,18 @@ def main() -> None:
 
     np.savez(HERE / "paged_kv_golden.npz", **out)
     host = host_script(paged, kveng)
-    (HERE / "host_golden.json").write_text(json.dumps({"meta": meta, "host": host}, indent=1, sort_keys=True))
+    # the positional surface of the reference's operators: parameter names in order, and which
+    # of them have defaults; the tests hold this package's operators to it
+    upd = load(ref, "ref_update_kv_buffer", "lite_llama/kernels/update_kv_buffer.py")
+    upi = load(ref, "ref_update_kv_index", "lite_llama/kernels/update_kv_index.py")
+    signatures = {}
+    for fn in (upd.update_kv_buffer, fdec.flash_decoding, chunk.paged_chunk_flash_attention,
+               nopad.flash_attention2_no_pad, upi.update_kv_index):
+        params = inspect.signature(fn).parameters
+        signatures[fn.__name__] = [[n, prm.default is not inspect.Parameter.empty, prm.kind.name]
+                                   for n, prm in params.items()]
+    (HERE / "host_golden.json").write_text(json.dumps({"meta": meta, "host": host, "signatures": signatures},
+                                                      indent=1, sort_keys=True))
     print("wrote", HERE / "paged_kv_golden.npz", (HERE / "paged_kv_golden.npz").stat().st_size, "bytes")
 
 

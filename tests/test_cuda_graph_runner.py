@@ -111,46 +111,179 @@ def test_failed_capture_falls_back_and_is_not_retried():
     assert r.capture_attempt_count == 1 and r.fallback_count == 2
 
 
+def test_replay_copies_nothing_when_the_caller_passes_the_recorded_tensors():
+    """Address-stable inputs are read in place: only tensors that moved are refreshed."""
+    model = FakeModel()
+    r = CudaGraphRunner(model, graph_api=FakeApi)
+    ids, pos = torch.tensor([[1], [2]]), torch.zeros(2, 1, dtype=torch.long)
+    info = _info([100, 90], [5, 6])
+    r(ids, pos, info)                                   # records private copies, refreshes all five
+    assert r.refresh_copy_count == 5
+    rec = r._graphs[(2, 128)]
+    # hand the runner its own recorded tensors back (what a pointer-stable executor amounts to)
+    stable = SimpleNamespace(b_seq_len=rec.inputs["b_seq_len"], cur_select_index=rec.inputs["cur_select_index"],
+                             b_req_idx=rec.inputs["b_req_idx"], max_actual_seq_len=100)
+    stable.b_seq_len += 1                               # "the device advanced them in place"
+    out = r(rec.inputs["input_ids"], rec.inputs["position_ids"], stable)
+    assert out.tolist() == [107.0, 99.0] and r.refresh_copy_count == 5 and r.replay_count == 2
+    stable.cur_select_index = torch.tensor([9, 9], dtype=torch.int32)     # one tensor moved: one copy
+    out = r(rec.inputs["input_ids"], rec.inputs["position_ids"], stable)
+    assert out.tolist() == [111.0, 102.0] and r.refresh_copy_count == 6
+
+
+class FakePending:
+    """Device half of a staged step: lengths + 1 on whatever info it is run on."""
+
+    def __init__(self):
+        self.runs = 0
+
+    def run(self, info):
+        self.runs += 1
+        lens = info.b_seq_len
+
+        def advance():
+            lens.add_(1)
+
+        if FakeApi.current is not None:      # under capture nothing executes: it is only recorded
+            FakeApi.current.advance = advance
+        else:
+            advance()
+
+
+class FakeGraphWithAdvance(FakeGraph):
+    def replay(self):
+        self.replays += 1
+        if getattr(self, "advance", None) is not None:
+            self.advance()
+        self.fn()
+
+
+def test_staged_step_is_advanced_exactly_once_by_the_graph_and_rebinds_on_a_new_batch():
+    class Api(FakeApi):
+        @staticmethod
+        def new_graph():
+            return FakeGraphWithAdvance()
+
+    model = FakeModel()
+    r = CudaGraphRunner(model, graph_api=Api)
+    ids, pos = torch.tensor([[1], [2]]), torch.zeros(2, 1, dtype=torch.long)
+    info = _info([100, 90], [5, 6])
+    for step in range(3):
+        info.pending_advance = FakePending()
+        info.max_actual_seq_len += 1
+        out = r(ids, pos, info)
+        # lengths advanced once per step, on the live tensor, and the model saw the advanced value
+        assert info.b_seq_len.tolist() == [101 + step, 91 + step]
+        assert out.tolist() == [101.0 + step + 5 + 1, 91.0 + step + 6 + 2]
+        assert info.pending_advance is None
+    assert (r.capture_count, r.replay_count, r.fallback_count, r.refresh_copy_count) == (1, 3, 0, 0)
+    # the batch changed: new metadata tensors -> the old graph is dropped and a new one recorded
+    info2 = _info([50, 60], [1, 2])
+    info2.pending_advance = FakePending()
+    info2.max_actual_seq_len += 1
+    out = r(ids, pos, info2)
+    assert info2.b_seq_len.tolist() == [51, 61] and out.tolist() == [53.0, 65.0]
+    assert (r.capture_count, r.rebind_count, r.refresh_copy_count) == (2, 1, 0)
+    # a step that was advanced eagerly (nothing pending) cannot use the advancing graph
+    info2.b_seq_len += 1
+    out = r(ids, pos, info2)
+    assert out.tolist() == [54.0, 66.0] and info2.b_seq_len.tolist() == [52, 62] and r.rebind_count == 2
+
+
+def test_last_bucket_of_a_narrow_table_still_captures():
+    """A table 1000 tokens wide: the 1024 bucket is recorded with the bound clamped to 1000."""
+    seen = []
+
+    class Model(FakeModel):
+        def forward(self, input_ids, position_ids, info):
+            if info.max_actual_seq_len > info.b_req_tokens_table.shape[1]:
+                raise ValueError("max_actual_seq_len exceeds the table width")
+            seen.append(info.max_actual_seq_len)
+            return super().forward(input_ids, position_ids, info)
+
+    r = CudaGraphRunner(Model(), graph_api=FakeApi)
+    info = _info([990], [3])
+    info.b_req_tokens_table = torch.zeros(4, 1000, dtype=torch.int32)
+    ids, pos = torch.tensor([[1]]), torch.zeros(1, 1, dtype=torch.long)
+    r(ids, pos, info)
+    assert (r.capture_count, r.fallback_count) == (1, 0) and set(seen) == {1000}
+    assert not r._failed_keys
+
+
 @pytest.mark.gpu
-@pytest.mark.parametrize("extend", ["extend_paged_requests", "extend_paged_requests_on_device"])
-def test_paged_decode_step_replays_in_cuda_graph(extend):
+@pytest.mark.parametrize("extend", ["extend_paged_requests", "extend_paged_requests_on_device",
+                                    "stage_paged_decode_step"])
+def test_paged_decode_step_replays_in_cuda_graph(extend, monkeypatch):
     """Two 'layers' of (append + paged decode) captured once, replayed over several steps while
-    the requests keep growing (metadata from the host, or advanced on the device); every replay
-    equals the eager result."""
+    the requests keep growing.  Metadata comes from the host path (new tensors every step: the
+    runner refreshes its recorded copies), from the device path run eagerly, or from a staged
+    step whose device half is the graph's first node: then the graph reads the live tensors and
+    the runner issues no copy at all between replays.  Every replay equals an eager
+    twin driven through the host path."""
     dev, kvh, heads, layers = "cuda:0", 2, 16, 2
-    ex = PagedKVExecutor(layers, kvh, 128, 512, 8, 1024, page_size=16, device=dev)
-    for buf in ex.kv_mem_manager.gpu_kv_buffer:
-        buf.copy_(W.hash_normal_fp16(5, tuple(buf.shape), 1))
+    twins = [PagedKVExecutor(layers, kvh, 128, 512, 8, 1024, page_size=16, device=dev) for _ in range(2)]
+    for ex in twins:
+        for li, buf in enumerate(ex.kv_mem_manager.gpu_kv_buffer):
+            buf.copy_(W.hash_normal_fp16(5 + li, tuple(buf.shape), 1))
+    ex, ref = twins
     ids = ex.reserve_paged_requests([37, 100, 64, 5])
+    assert ref.reserve_paged_requests([37, 100, 64, 5]) == ids
     scale = 1.0 / math.sqrt(128)
 
-    class Model:
-        def forward(self, input_ids, position_ids, info):
-            saved, ex.atten_info = ex.atten_info, info
-            try:
-                x = xq
-                for layer in range(layers):
-                    x = ex.token_forward(x, xk, xv, layer, scale)
-                return x
-            finally:
-                ex.atten_info = saved
+    def model_on(executor):
+        class Model:
+            def forward(self, input_ids, position_ids, info):
+                saved, executor.atten_info = executor.atten_info, info
+                try:
+                    x = xq
+                    for layer in range(layers):
+                        x = executor.token_forward(x, xk, xv, layer, scale)
+                    return x
+                finally:
+                    executor.atten_info = saved
+        return Model()
 
-    runner = CudaGraphRunner(Model(), "harness")
-    eager = Model()
+    runner = CudaGraphRunner(model_on(ex), "harness")
+    eager = model_on(ref)
     xq = torch.empty(4, heads, 128, dtype=torch.float16, device=dev)      # static graph inputs
     xk = torch.empty(4, kvh, 128, dtype=torch.float16, device=dev)
     xv = torch.empty(4, kvh, 128, dtype=torch.float16, device=dev)
     inp = torch.zeros(4, 1, dtype=torch.long, device=dev)
+    copies = {"n": 0}
+    real_copy = torch.Tensor.copy_
+
+    def counting_copy(self, *a, **k):
+        copies["n"] += 1
+        return real_copy(self, *a, **k)
+
+    steady_copies = 0
     for step in range(20):                                   # every row crosses a page boundary
         getattr(ex, extend)(ids)
+        ref.extend_paged_requests(ids)
         xq.copy_(W.hash_normal_fp16(50 + step, (4, heads, 128), 1))
         xk.copy_(W.hash_normal_fp16(50 + step, (4, kvh, 128), 2))
         xv.copy_(W.hash_normal_fp16(50 + step, (4, kvh, 128), 3))
-        want = eager.forward(inp, inp, ex.atten_info).clone()
-        got = runner(inp, inp, ex.atten_info)
+        want = eager.forward(inp, inp, ref.atten_info).clone()
+        copies["n"] = 0
+        with monkeypatch.context() as m:
+            m.setattr(torch.Tensor, "copy_", counting_copy)
+            got = runner(inp, inp, ex.atten_info)
+        if step >= 2:
+            steady_copies += copies["n"]
         torch.cuda.synchronize()
         # the bucketed length bound may split the page line differently from the exact one
         assert float((got.float() - want.float()).abs().max()) <= 2e-3, step
-    assert (runner.capture_count, runner.replay_count, runner.fallback_count) == (1, 20, 0)
+        assert torch.equal(ex.atten_info.b_seq_len.cpu(), ref.atten_info.b_seq_len.cpu())
+    for a, b in zip(ex.kv_mem_manager.gpu_kv_buffer, ref.kv_mem_manager.gpu_kv_buffer):
+        assert torch.equal(a, b)
+    assert (runner.replay_count, runner.fallback_count) == (20, 0)
+    if extend != "stage_paged_decode_step":
+        # recorded on private copies, as the reference does: ids, positions and the three metadata
+        # tensors are refreshed before every replay
+        assert runner.capture_count == 1 and steady_copies == 18 * 5 and runner.refresh_copy_count == 20 * 5
+    else:
+        # step 1: host path (activates the batch), graph without advance; step 2: first staged step,
+        # that graph is replaced by one that advances; from then on no copy of any kind
+        assert runner.capture_count == 2 and runner.rebind_count == 1 and steady_copies == 0
     from llama_lite_npu_b200 import kernels
     kernels.check_status(0)

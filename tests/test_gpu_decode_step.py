@@ -259,3 +259,44 @@ def test_captured_chain_of_whole_sequence_steps():
             assert torch.equal(lens_d.cpu(), lens_h)
     kernels.check_status(0)
     assert _counters_are_zero()
+
+
+def test_debug_mode_checks_index_tensors_on_the_host_before_launch():
+    """Debug mode: an out-of-range slot, two tokens aimed at one slot with different rows, a
+    length beyond the stated maximum and a request id outside the table are all refused on the
+    host; two tokens that write the same row to one slot (a shared partial page) are allowed."""
+    src, slots, pool = G.build_append("append_prefill")
+    src, slots, pool = src.to(DEV), slots.to(DEV), pool.to(DEV)
+    kernels.set_debug(True)
+    try:
+        kernels.update_kv_buffer(src, slots, pool)                       # clean input passes
+        dup = slots.clone()
+        dup[7] = dup[3]
+        with pytest.raises(ValueError, match="different K/V rows"):
+            kernels.update_kv_buffer(src, dup, pool)
+        same = src.clone()
+        same[7] = same[3]
+        before = pool.clone()
+        kernels.update_kv_buffer(same, dup, pool)                        # identical payloads: fine
+        before[dup.long()] = same
+        assert torch.equal(pool, before)
+        far = slots.clone()
+        far[0] = pool.shape[0]
+        with pytest.raises(ValueError, match="outside the pool"):
+            kernels.update_kv_buffer(src, far, pool)
+        rows = src.shape[1]
+        with pytest.raises(ValueError, match="different K/V rows"):
+            kernels.update_kv_buffer_split(src[:, : rows // 2].contiguous(), src[:, rows // 2:].contiguous(), dup, pool)
+        c = G.build_decode("decode_gqa8_small")
+        lens = c.seq_lens_t.clone()
+        lens[1] = c.max_len + 1
+        with pytest.raises(ValueError, match="length"):
+            kernels.flash_decoding(c.q.to(DEV), c.pool.to(DEV)[:, :2], c.pool.to(DEV)[:, 2:], SCALE,
+                                   c.block_table.to(DEV), lens.to(DEV), c.max_len, table_kind="block")
+        with pytest.raises(ValueError, match="request id"):
+            kernels.flash_decoding(c.q.to(DEV), c.pool.to(DEV)[:, :2], c.pool.to(DEV)[:, 2:], SCALE,
+                                   c.block_table.to(DEV), c.seq_lens_t.to(DEV), c.max_len, table_kind="block",
+                                   b_req_idx=torch.tensor([0, 1, 2, 3, 9], dtype=torch.int32, device=DEV))
+    finally:
+        kernels.set_debug(False)
+    kernels.check_status(0)
