@@ -169,6 +169,20 @@ int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i
                           int32_t* status, void* stream);
 
 /*
+ * table[offsets[i]] = values[i] for i in [0, n): a few entries of a device table (block table,
+ * token table, page counts) that changed on the host.  offsets_host and values_host are HOST
+ * arrays; they are copied into the launch arguments, so they may be reused as soon as the call
+ * returns and nothing crosses PCIe as a separate copy.  Replaces the small per-request
+ * host-to-device writes of the reference's extend_req / alloc_req
+ * (lite_llama/executor/paged_attention.py:209-212, :354-357).  Offsets are element offsets into
+ * `table` (table_elems elements); one outside it is refused with B200KV_EINVAL and nothing is
+ * launched.  Any n; 96 entries go into one launch.
+ */
+int b200kv_table_patch(int32_t* table, int64_t table_elems,
+                       const int64_t* offsets_host, const int32_t* values_host, int64_t n,
+                       void* stream);
+
+/*
  * req_to_token_indexs[b_req_idx[i]][b_seq_len[i] - 1] = select_index[i] for i in [0, n).
  * Replaces update_kv_index (lite_llama/kernels/update_kv_index.py:42-74, kernel :6-38), the
  * token-table write of the non-paged decode path

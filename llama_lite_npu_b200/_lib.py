@@ -45,6 +45,7 @@ _SIGNATURES = {
          c_void_p, c_int64, c_int,                       # token table
          c_int, c_int, c_int64, c_void_p, c_void_p],
     ),
+    "b200kv_table_patch": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "b200kv_update_kv_index": (
         c_int,
         [c_void_p, c_int64, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,

@@ -139,6 +139,11 @@ int b200kv_decode_advance(const int32_t* req_ids, void* seq_lens, int seq_lens_i
   return b200kv::decode_advance(a, static_cast<cudaStream_t>(stream));
 }
 
+int b200kv_table_patch(int32_t* table, int64_t table_elems, const int64_t* offsets_host,
+                       const int32_t* values_host, int64_t n, void* stream) {
+  return b200kv::table_patch(table, table_elems, offsets_host, values_host, n, static_cast<cudaStream_t>(stream));
+}
+
 int b200kv_update_kv_index(int32_t* req_to_token_indexs, int64_t row_stride, int64_t col_stride,
                            int rows, int cols, const int32_t* b_req_idx, const void* b_seq_len,
                            int seq_lens_i64, const int32_t* select_index, int n, int32_t* status,

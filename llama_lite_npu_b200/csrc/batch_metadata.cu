@@ -98,7 +98,59 @@ __global__ void __launch_bounds__(128) update_kv_index_kernel(IndexParams p) {
   p.table[row * p.row_stride + col * p.col_stride] = p.select_index[i];
 }
 
+// A handful of table entries changed on the host (a sequence crossed a page boundary, a request
+// was admitted): the (offset, value) pairs travel as kernel ARGUMENTS, so there is no staging
+// buffer to keep alive and no host-to-device copy to order, just one small launch.
+constexpr int kPatchMax = 96;
+struct PatchParams {
+  int32_t* table;
+  int64_t elems;
+  int n;
+  int64_t off[kPatchMax];
+  int32_t val[kPatchMax];
+};
+
+__global__ void __launch_bounds__(kPatchMax) table_patch_kernel(const __grid_constant__ PatchParams p) {
+  cudaGridDependencySynchronize();
+  cudaTriggerProgrammaticLaunchCompletion();
+  const int i = threadIdx.x;
+  if (i >= p.n) return;
+  const int64_t off = p.off[i];
+  if (off >= 0 && off < p.elems) p.table[off] = p.val[i];
+}
+
 }  // namespace
+
+int table_patch(int32_t* table, int64_t elems, const int64_t* offsets_host, const int32_t* values_host,
+                int64_t n, cudaStream_t stream) {
+  if (n < 0 || elems <= 0) return B200KV_EINVAL;
+  if (n == 0) return B200KV_OK;
+  if (!table || !offsets_host || !values_host) return B200KV_EINVAL;
+  for (int64_t i = 0; i < n; ++i)
+    if (offsets_host[i] < 0 || offsets_host[i] >= elems) return B200KV_EINVAL;   // nothing launched
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  for (int64_t done = 0; done < n; done += kPatchMax) {
+    PatchParams p{};
+    p.table = table;
+    p.elems = elems;
+    p.n = static_cast<int>(n - done < kPatchMax ? n - done : kPatchMax);
+    for (int i = 0; i < p.n; ++i) {
+      p.off[i] = offsets_host[done + i];
+      p.val[i] = values_host[done + i];
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(kPatchMax);
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, table_patch_kernel, p);
+    if (e != cudaSuccess) return record_cuda_error(e);
+  }
+  return check_launch();
+}
 
 int update_kv_index(int32_t* table, int64_t row_stride, int64_t col_stride, int rows, int cols,
                     const int32_t* req_ids, const void* seq_lens, int seq_lens_i64,

@@ -59,6 +59,9 @@ struct AdvanceArgs {
   int32_t* status;
 };
 int decode_advance(const AdvanceArgs& a, cudaStream_t stream);
+// table[offsets[i]] = values[i]; offsets / values are HOST arrays, passed to the kernel as arguments.
+int table_patch(int32_t* table, int64_t elems, const int64_t* offsets_host, const int32_t* values_host,
+                int64_t n, cudaStream_t stream);
 int update_kv_index(int32_t* table, int64_t row_stride, int64_t col_stride, int rows, int cols,
                     const int32_t* req_ids, const void* seq_lens, int seq_lens_i64,
                     const int32_t* select_index, int n, int32_t* status, cudaStream_t stream);

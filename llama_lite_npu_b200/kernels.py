@@ -296,6 +296,25 @@ def update_kv_index(req_to_token_indexs: torch.Tensor, b_req_idx: torch.Tensor, 
     _after_call(dev)
 
 
+def patch_table(table: torch.Tensor, offsets, values) -> None:
+    """``table.view(-1)[offsets[i]] = values[i]``: a few entries of an int32 device table that
+    changed on the host, sent as launch arguments (no staging buffer, no separate copy).
+    ``offsets`` (int64) and ``values`` (int32) are host numpy arrays."""
+    import numpy as np
+
+    dev = _device_index(table)
+    _require(table.dtype == torch.int32 and table.is_contiguous(), "table must be a contiguous int32 tensor")
+    off = np.ascontiguousarray(offsets, dtype=np.int64)
+    val = np.ascontiguousarray(values, dtype=np.int32)
+    _require(off.shape == val.shape and off.ndim == 1, "offsets and values must be 1-D and equally long")
+    if off.shape[0] == 0:
+        return
+    with _on_device(dev):
+        rc = _lib.lib().b200kv_table_patch(table.data_ptr(), table.numel(), off.ctypes.data, val.ctypes.data,
+                                           off.shape[0], _stream(dev))
+    _lib.check(rc)
+
+
 @torch.no_grad()
 def advance_decode_metadata(b_seq_len: torch.Tensor, cur_select_index: torch.Tensor,
                             b_req_block_table: torch.Tensor, page_size: int, num_pages: int, *,

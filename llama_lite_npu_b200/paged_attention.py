@@ -63,6 +63,8 @@ class PagedKVCacheManager:
         self.page_refcount = torch.zeros(num_pages, dtype=torch.int32, device="cpu")
         self.num_free_pages = num_pages
         self._free_heap: list[int] = list(range(num_pages))  # already a valid min-heap
+        self._free_np = self.page_free.numpy()          # views of the two tensors above
+        self._refcount_np = self.page_refcount.numpy()
 
     # -- allocation ---------------------------------------------------------
     def alloc(self, num_tokens: int) -> Optional[torch.Tensor]:
@@ -76,6 +78,17 @@ class PagedKVCacheManager:
         self.page_refcount[pages] = 1
         self.num_free_pages -= num_needed
         return pages
+
+    def alloc_one(self) -> Optional[int]:
+        """The lowest free page id (one reference taken) or ``None``: ``alloc(page_size)`` without
+        building a tensor, for the decode step that crosses a page boundary."""
+        if self.num_free_pages < 1:
+            return None
+        page = heapq.heappop(self._free_heap)
+        self._free_np[page] = False
+        self._refcount_np[page] = 1
+        self.num_free_pages -= 1
+        return page
 
     def add_ref(self, page_indices: torch.Tensor):
         """One more owner for pages that are already allocated."""
@@ -156,9 +169,22 @@ class PagedReqTokensManager:
         self._dev_page_counts = (torch.zeros(max_requests, dtype=torch.int32, device=device)
                                  if on_gpu else self._host_page_counts)
         self._dirty_counts = False
+        self._dirty_count_rows: set[int] = set()
         self._dirty_tokens: list[tuple[int, int, int]] = []  # (row, start, end) token spans
         self._dirty_blocks: list[tuple[int, int, int]] = []  # (row, start, end) page spans
 
+        # numpy views of the host mirrors, and per-row arrays behind the two dictionaries below:
+        # the decode step reads and advances whole batches of rows through these, not through
+        # per-request dictionary lookups
+        self._tokens_np = self._host_tokens.numpy()
+        self._blocks_np = self._host_blocks.numpy()
+        self._counts_np = self._host_page_counts.numpy()
+        self._len_np = np.zeros(max_requests, dtype=np.int64)
+        self._pages64 = torch.zeros((max_requests, self.max_pages_per_req), dtype=torch.long)
+        self._pages64_np = self._pages64.numpy()
+        self._batch_rows = None      # (request ids, the same as an int64 array, as a list)
+
+        # request id -> its pages in logical order (a view of a row of _pages64) / its token count
         self.req_page_table: dict[int, torch.Tensor] = {}
         self.req_token_count: dict[int, int] = {}
         self.req_active = torch.zeros(max_requests, dtype=torch.bool, device="cpu")
@@ -189,10 +215,16 @@ class PagedReqTokensManager:
             self._dirty_tokens.clear()
             self._dirty_blocks.clear()
             self._dirty_counts = False
+            self._dirty_count_rows.clear()
+            return
+        n_dirty = sum(e - s for _, s, e in self._dirty_tokens) + sum(e - s for _, s, e in self._dirty_blocks)
+        if n_dirty <= self._PATCH_LIMIT:
+            self._flush_small()
             return
         if self._dirty_counts:
             self._dev_page_counts.copy_(self._host_page_counts, non_blocking=True)
             self._dirty_counts = False
+            self._dirty_count_rows.clear()
         for dirty, host, dev in (
             (self._dirty_tokens, self._host_tokens, self._dev_tokens),
             (self._dirty_blocks, self._host_blocks, self._dev_blocks),
@@ -210,6 +242,37 @@ class PagedReqTokensManager:
             )
             dirty.clear()
 
+    _PATCH_LIMIT = 192   # table entries up to which edits travel as launch arguments
+
+    def _flush_small(self) -> None:
+        """A few edited entries (the usual decode step: some sequences crossed a page boundary):
+        one small launch per edited table with the (offset, value) pairs as its arguments."""
+        from . import kernels
+
+        for dirty, host_np, dev in ((self._dirty_tokens, self._tokens_np, self._dev_tokens),
+                                    (self._dirty_blocks, self._blocks_np, self._dev_blocks)):
+            if not dirty:
+                continue
+            width = host_np.shape[1]
+            off = np.concatenate([np.arange(row * width + s, row * width + e, dtype=np.int64)
+                                  for row, s, e in dirty])
+            kernels.patch_table(dev, off, host_np.reshape(-1)[off])
+            dirty.clear()
+        if self._dirty_counts:
+            if self._dirty_count_rows and len(self._dirty_count_rows) <= self._PATCH_LIMIT:
+                rows = np.fromiter(self._dirty_count_rows, dtype=np.int64, count=len(self._dirty_count_rows))
+                kernels.patch_table(self._dev_page_counts, rows, self._counts_np[rows])
+            else:
+                self._dev_page_counts.copy_(self._host_page_counts, non_blocking=True)
+            self._dirty_count_rows.clear()
+            self._dirty_counts = False
+
+    def _set_pages(self, req_idx: int, have: int, extra: torch.Tensor) -> None:
+        """Pages ``have ...`` of a request become ``extra``; its page list is a view of its row."""
+        n = have + len(extra)
+        self._pages64[req_idx, have:n] = extra
+        self.req_page_table[req_idx] = self._pages64[req_idx, :n]
+
     def _write_pages(self, req_idx: int, first_page: int) -> None:
         pages = self.req_page_table[req_idx]
         if first_page < len(pages):
@@ -217,6 +280,7 @@ class PagedReqTokensManager:
             self._dirty_blocks.append((req_idx, first_page, len(pages)))
         self._host_page_counts[req_idx] = len(pages)
         self._dirty_counts = True
+        self._dirty_count_rows.add(req_idx)
 
     def _write_tokens(self, req_idx: int, start: int, end: int) -> None:
         if end <= start:
@@ -245,8 +309,9 @@ class PagedReqTokensManager:
 
     def _adopt(self, req_idx: int, pages: torch.Tensor, num_tokens: int) -> None:
         self.free_req_indices.remove(req_idx)
-        self.req_page_table[req_idx] = pages
+        self._set_pages(req_idx, 0, pages)
         self.req_token_count[req_idx] = num_tokens
+        self._len_np[req_idx] = num_tokens
         self.req_active[req_idx] = True
         mapped = self.page_mgr.build_token_table(pages, num_tokens, self._host_tokens, req_idx)
         if mapped:
@@ -279,7 +344,7 @@ class PagedReqTokensManager:
         extra = self.page_mgr.alloc((need - have) * ps)
         if extra is None:
             return False
-        self.req_page_table[req_idx] = torch.cat([self.req_page_table[req_idx], extra])
+        self._set_pages(req_idx, have, extra)
         self._write_pages(req_idx, have)
         return True
 
@@ -344,10 +409,11 @@ class PagedReqTokensManager:
             extra = self.page_mgr.alloc((need - have) * ps)
             if extra is None:
                 return False
-            self.req_page_table[req_idx] = torch.cat([self.req_page_table[req_idx], extra])
+            self._set_pages(req_idx, have, extra)
             self._write_pages(req_idx, have)
         self._write_tokens(req_idx, cur, new_total)
         self.req_token_count[req_idx] = new_total
+        self._len_np[req_idx] = new_total
         return True
 
     def extend_batch_for_device(self, req_indices) -> Optional[int]:
@@ -358,31 +424,39 @@ class PagedReqTokensManager:
         whose extension failed (earlier requests of the batch stay extended, as with
         ``extend_req`` in a loop)."""
         ps = self.page_mgr.page_size
-        counts = self.req_token_count
-        n = len(req_indices)
-        rows = np.fromiter(req_indices, dtype=np.int64, count=n)
-        cur = np.fromiter((counts[r] for r in req_indices), dtype=np.int64, count=n)
+        cached = self._batch_rows
+        if cached is None or (cached[0] is not req_indices and cached[0] != tuple(req_indices)):
+            key = tuple(int(r) for r in req_indices)
+            cached = self._batch_rows = (key, np.array(key, dtype=np.int64), list(key))
+        _, rows, row_list = cached
+        cur = self._len_np[rows]
         failed = None
         # the rare cases, in batch order: a row at its maximum length, or one that needs a page
-        special = np.flatnonzero((cur >= self.max_seq_len) | (cur // ps >= self._host_page_counts.numpy()[rows]))
+        special = np.flatnonzero((cur >= self.max_seq_len) | (cur // ps >= self._counts_np[rows]))
         for i in special.tolist():
-            req_idx = int(rows[i])
+            req_idx = row_list[i]
             if cur[i] + 1 > self.max_seq_len:
                 failed = i
                 break
-            have = len(self.req_page_table[req_idx])
-            extra = self.page_mgr.alloc(ps)
-            if extra is None:
+            page = self.page_mgr.alloc_one()
+            if page is None:
                 failed = i
                 break
-            self.req_page_table[req_idx] = torch.cat([self.req_page_table[req_idx], extra])
-            self._write_pages(req_idx, have)
+            have = int(self._counts_np[req_idx])
+            self._pages64_np[req_idx, have] = page
+            self._blocks_np[req_idx, have] = page
+            self._counts_np[req_idx] = have + 1
+            self.req_page_table[req_idx] = self._pages64[req_idx, : have + 1]
+            self._dirty_blocks.append((req_idx, have, have + 1))
+            self._dirty_counts = True
+            self._dirty_count_rows.add(req_idx)
         if failed is not None:
-            rows, cur = rows[:failed], cur[:failed]
-        for r in rows.tolist():
+            rows, cur, row_list = rows[:failed], cur[:failed], row_list[:failed]
+        self._len_np[rows] = cur + 1
+        counts = self.req_token_count
+        for r in row_list:
             counts[r] += 1
-        blocks, tokens = self._host_blocks.numpy(), self._host_tokens.numpy()
-        tokens[rows, cur] = blocks[rows, cur // ps] * ps + cur % ps
+        self._tokens_np[rows, cur] = self._blocks_np[rows, cur // ps] * ps + cur % ps
         return None if failed is None else int(req_indices[failed])
 
     def get_token_indices(self, req_idx: int, num_tokens: Optional[int] = None) -> torch.Tensor:
@@ -396,8 +470,10 @@ class PagedReqTokensManager:
             self.page_mgr.free(self.req_page_table[req_idx])
             del self.req_page_table[req_idx]
             del self.req_token_count[req_idx]
+            self._len_np[req_idx] = 0
             self._host_page_counts[req_idx] = 0
             self._dirty_counts = True
+            self._dirty_count_rows.add(req_idx)
         self.req_active[req_idx] = False
         if req_idx not in self.free_req_indices:
             bisect.insort(self.free_req_indices, req_idx)

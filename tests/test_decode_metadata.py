@@ -166,3 +166,27 @@ def test_update_kv_index_matches_statement(built_lib):
     with pytest.raises(RuntimeError, match="length"):
         kernels.check_status(0)
     assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.gpu
+def test_table_patch_writes_exactly_the_named_entries(built_lib):
+    import numpy as np
+
+    from llama_lite_npu_b200 import kernels
+
+    dev = "cuda:0"
+    table = torch.arange(7 * 300, dtype=torch.int32).view(7, 300)
+    want = table.clone()
+    rng = np.random.default_rng(3)
+    for n in (1, 5, 96, 97, 250):                       # one launch holds 96 entries
+        off = rng.choice(table.numel(), size=n, replace=False).astype(np.int64)
+        val = rng.integers(-5, 1 << 30, size=n).astype(np.int32)
+        got = want.to(dev)
+        kernels.patch_table(got, off, val)
+        want.view(-1)[torch.from_numpy(off)] = torch.from_numpy(val)
+        assert torch.equal(got.cpu(), want)
+    kernels.patch_table(got, np.zeros(0, np.int64), np.zeros(0, np.int32))     # nothing to do
+    with pytest.raises(ValueError):                                               # offset outside the table
+        kernels.patch_table(got, np.array([table.numel()], np.int64), np.array([1], np.int32))
+    assert torch.equal(got.cpu(), want)
+    kernels.check_status(0)
