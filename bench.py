@@ -372,6 +372,7 @@ def decode_bench(cfg, dev, steps, warmup, timer, prologue=False, with_e2e=True):
         g.manual_seed(cfg.seed * 977 + i)
         p.normal_(generator=g)
     out = torch.empty_like(case.q)
+    torch.cuda.synchronize()     # the fills ran on the default stream; the steps run on the timer's own
 
     if prologue:
         # the step starts from the raw projections: QK-RMSNorm + rotary embedding + append, fused
@@ -423,37 +424,63 @@ def decode_bench(cfg, dev, steps, warmup, timer, prologue=False, with_e2e=True):
                 cur = (cur + 15) // 16 * 16
                 offs[name] = (cur, t.numel() * t.element_size())
                 cur += t.numel() * t.element_size()
-            h_in = torch.empty(cur, dtype=torch.uint8).pin_memory()
-            d_in = torch.empty(cur, dtype=torch.uint8, device=dev)
+            # Two staging sets and three streams: step i+1's inputs cross PCIe while step i computes,
+            # and step i's result goes back while step i+1 computes.  Every step still makes both
+            # copies inside the timed region.
+            depth = 2
+            h_in = [torch.empty(cur, dtype=torch.uint8).pin_memory() for _ in range(depth)]
+            d_in = [torch.empty(cur, dtype=torch.uint8, device=dev) for _ in range(depth)]
+            h_out = [torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory() for _ in range(depth)]
+            d_out = [torch.empty_like(case.q) for _ in range(depth)]
 
             def view(buf, name, like):
                 o, n = offs[name]
                 return buf[o:o + n].view(like.dtype).view(like.shape)
 
-            for name, t in parts:
-                view(h_in, name, t).copy_(t.cpu())
-            d_q, d_kv = view(d_in, "q", case.q), view(d_in, "kv", case.new_kv)
-            d_lens, d_slots = view(d_in, "lens", case.seq_lens_t), view(d_in, "slots", case.slots)
-            h_out = torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory()
-            d_out = torch.empty_like(case.q)
+            for hb in h_in:
+                for name, t in parts:
+                    view(hb, name, t).copy_(t.cpu())
+            views = [(view(b, "q", case.q), view(b, "kv", case.new_kv), view(b, "lens", case.seq_lens_t),
+                      view(b, "slots", case.slots)) for b in d_in]
+            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            ev_in = [torch.cuda.Event() for _ in range(depth)]      # inputs of the slot are on the device
+            ev_done = [torch.cuda.Event() for _ in range(depth)]    # the slot's kernel has finished
+            ev_out = [torch.cuda.Event() for _ in range(depth)]     # the slot's result has left the device
 
             def e2e_step(i):
-                d_in.copy_(h_in, non_blocking=True)
+                k = i % depth
+                d_q, d_kv, d_lens, d_slots = views[k]
+                s_in.wait_event(ev_done[k])            # the kernel that last read this slot's inputs is done
+                with torch.cuda.stream(s_in):
+                    d_in[k].copy_(h_in[k], non_blocking=True)
+                    ev_in[k].record(s_in)
+                stream.wait_event(ev_in[k])
+                stream.wait_event(ev_out[k])           # the slot's previous result has been copied out
                 kernels.append_flash_decoding(d_kv, d_slots, pools[i % layers], d_q, scale, case.block_table,
-                                              d_lens, case.max_len, table_kind="block", out=d_out)
-                h_out.copy_(d_out, non_blocking=True)
+                                              d_lens, case.max_len, table_kind="block", out=d_out[k])
+                ev_done[k].record(stream)
+                s_out.wait_event(ev_done[k])
+                with torch.cuda.stream(s_out):
+                    h_out[k].copy_(d_out[k], non_blocking=True)
+                    ev_out[k].record(s_out)
 
-            for i in range(3):
+            def drain():
+                stream.wait_stream(s_in)
+                stream.wait_stream(s_out)
+
+            for i in range(4):
                 e2e_step(i)
+            drain()
             timer.barrier()
             x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             x0.record(stream)
             for i in range(steps):
                 e2e_step(i)
+            drain()
             x1.record(stream)
             timer.barrier()
             res["ms_e2e_total"] = x0.elapsed_time(x1)
-            res["h2d"], res["d2h"] = cur, h_out.numel() * h_out.element_size()
+            res["h2d"], res["d2h"] = cur, h_out[0].numel() * h_out[0].element_size()
         kernels.check_status(torch.device(dev).index)
     del pools
     return res
@@ -470,6 +497,7 @@ def prefill_bench(cfg, dev, steps, warmup, timer, with_e2e=True):
     for name in ("pool", "block_table", "req_ids", "q_start", "ctx_lens_t", "q_lens_t", "q", "new_kv", "slots"):
         setattr(case, name, getattr(case, name).to(dev))
     stream = timer.stream
+    torch.cuda.synchronize()     # inputs were copied on the default stream; the steps run on the timer's own
 
     def attend(_i=0):
         return kernels.paged_chunk_flash_attention(

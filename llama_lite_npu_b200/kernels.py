@@ -22,6 +22,7 @@ from __future__ import annotations
 import os
 from typing import Optional
 
+import numpy as _np
 import torch
 
 from . import _lib
@@ -122,7 +123,13 @@ def _debug_check_lengths(lens: torch.Tensor, max_len: int, rows: Optional[torch.
         raise ValueError(f"{what}: a request id lies outside the table's {table_rows} rows")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(device_index: int) -> int:
+    """Handle of torch's current stream on the device (the cheap accessor when torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(device_index)
     return torch.cuda.current_stream(device_index).cuda_stream
 
 
@@ -300,22 +307,22 @@ def patch_table(table: torch.Tensor, offsets, values) -> None:
     """``table.view(-1)[offsets[i]] = values[i]``: a few entries of an int32 device table that
     changed on the host, sent as launch arguments (no staging buffer, no separate copy).
     ``offsets`` (int64) and ``values`` (int32) are host numpy arrays."""
-    import numpy as np
-
     dev = _device_index(table)
-    _require(table.dtype == torch.int32 and table.is_contiguous(), "table must be a contiguous int32 tensor")
-    off = np.ascontiguousarray(offsets, dtype=np.int64)
-    val = np.ascontiguousarray(values, dtype=np.int32)
-    _require(off.shape == val.shape and off.ndim == 1, "offsets and values must be 1-D and equally long")
+    if table.dtype != torch.int32 or not table.is_contiguous():
+        raise ValueError("table must be a contiguous int32 tensor")
+    off = _np.ascontiguousarray(offsets, dtype=_np.int64)
+    val = _np.ascontiguousarray(values, dtype=_np.int32)
+    if off.shape != val.shape or off.ndim != 1:
+        raise ValueError("offsets and values must be 1-D and equally long")
     if off.shape[0] == 0:
         return
     with _on_device(dev):
         rc = _lib.lib().b200kv_table_patch(table.data_ptr(), table.numel(), off.ctypes.data, val.ctypes.data,
                                            off.shape[0], _stream(dev))
-    _lib.check(rc)
+    if rc != 0:
+        _lib.check(rc)
 
 
-@torch.no_grad()
 def advance_decode_metadata(b_seq_len: torch.Tensor, cur_select_index: torch.Tensor,
                             b_req_block_table: torch.Tensor, page_size: int, num_pages: int, *,
                             b_req_idx: Optional[torch.Tensor] = None,
@@ -330,36 +337,42 @@ def advance_decode_metadata(b_seq_len: torch.Tensor, cur_select_index: torch.Ten
     (``lite_llama/executor/paged_attention.py:287-359``); the page of the new token must already
     be in the block table (``page_counts`` lets the kernel check that)."""
     dev = _device_index(b_req_block_table)
-    _, i64 = _lens_arg(b_seq_len, "b_seq_len")
+    lens_dtype = b_seq_len.dtype
+    if (lens_dtype != torch.int64 and lens_dtype != torch.int32) or b_seq_len.dim() != 1 \
+            or not b_seq_len.is_contiguous():
+        raise ValueError("b_seq_len must be a contiguous 1-D int32 or int64 tensor")
     n = b_seq_len.shape[0]
-    _require(cur_select_index.dtype == torch.int32 and cur_select_index.shape == (n,)
-             and cur_select_index.is_contiguous(), "cur_select_index must be int32 [batch], contiguous")
-    _require(b_req_block_table.dtype == torch.int32 and b_req_block_table.dim() == 2
-             and b_req_block_table.stride(1) == 1, "b_req_block_table must be a 2-D int32 tensor")
+    if cur_select_index.dtype != torch.int32 or cur_select_index.shape != (n,) or not cur_select_index.is_contiguous():
+        raise ValueError("cur_select_index must be int32 [batch], contiguous")
+    blk = b_req_block_table
+    if blk.dtype != torch.int32 or blk.dim() != 2 or blk.stride(1) != 1:
+        raise ValueError("b_req_block_table must be a 2-D int32 tensor")
+    blk_rows, blk_cols = blk.shape
     for t, name in ((b_req_idx, "b_req_idx"), (page_counts, "page_counts")):
-        _require(t is None or (t.dtype == torch.int32 and t.dim() == 1 and t.is_contiguous()),
-                 f"{name} must be a contiguous 1-D int32 tensor")
-    _require(b_req_idx is None or b_req_idx.shape[0] == n, "b_req_idx must have one entry per sequence")
-    _require(page_counts is None or page_counts.shape[0] == b_req_block_table.shape[0],
-             "page_counts must have one entry per table row")
+        if t is not None and (t.dtype != torch.int32 or t.dim() != 1 or not t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous 1-D int32 tensor")
+    if b_req_idx is not None and b_req_idx.shape[0] != n:
+        raise ValueError("b_req_idx must have one entry per sequence")
+    if page_counts is not None and page_counts.shape[0] != blk_rows:
+        raise ValueError("page_counts must have one entry per table row")
     tt = b_req_tokens_table
-    _require(tt is None or (tt.dtype == torch.int32 and tt.dim() == 2 and tt.stride(1) == 1
-                            and tt.shape[0] == b_req_block_table.shape[0]),
-             "b_req_tokens_table must be a 2-D int32 tensor with the block table's rows")
+    if tt is not None and (tt.dtype != torch.int32 or tt.dim() != 2 or tt.stride(1) != 1 or tt.shape[0] != blk_rows):
+        raise ValueError("b_req_tokens_table must be a 2-D int32 tensor with the block table's rows")
     if n == 0:
         return
     with _on_device(dev):
         rc = _lib.lib().b200kv_decode_advance(
-            0 if b_req_idx is None else b_req_idx.data_ptr(), b_seq_len.data_ptr(), i64,
-            cur_select_index.data_ptr(), b_req_block_table.data_ptr(), b_req_block_table.stride(0),
-            b_req_block_table.shape[0], b_req_block_table.shape[1],
+            0 if b_req_idx is None else b_req_idx.data_ptr(), b_seq_len.data_ptr(), lens_dtype == torch.int64,
+            cur_select_index.data_ptr(), blk.data_ptr(), blk.stride(0), blk_rows, blk_cols,
             0 if page_counts is None else page_counts.data_ptr(),
             0 if tt is None else tt.data_ptr(), 0 if tt is None else tt.stride(0),
             0 if tt is None else tt.shape[1], n, int(page_size), int(num_pages),
             status_tensor(dev).data_ptr(), _stream(dev),
         )
-    _lib.check(rc)
-    _after_call(dev)
+    if rc != 0:
+        _lib.check(rc)
+    if _DEBUG:
+        check_status(dev)
 
 
 @torch.no_grad()
@@ -420,40 +433,44 @@ def fused_qk_norm_rope_append(xq: torch.Tensor, xkv: torch.Tensor, q_norm_weight
     return out
 
 
-def _decode_call(new_rows, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len, max_actual_seq_len,
+def _decode_call(new_rows, slots, q, kv, qk_scale, tbl, b_seq_len, max_actual_seq_len,
                  b_req_idx, table_kind, page_size, out, metadata_fresh):
-    """Shared body of the decode operators; ``new_rows`` is ``None`` or ``(k_ptr, v_ptr, k_token_stride,
-    v_token_stride)`` of the step's new K/V rows for the fused append."""
+    """Shared body of the decode operators.  ``kv`` is ``(k_ptr, v_ptr, token_stride, head_stride,
+    pool_tokens, kv_heads, head_dim)`` of the pool views; ``new_rows`` is ``None`` or ``(k_ptr,
+    v_ptr, k_token_stride, v_token_stride)`` of the step's new K/V rows for the fused append.
+    This runs once per layer per decode step, so it reads each tensor attribute once and makes
+    one library call."""
     dev = _device_index(q)
-    _require(q.dtype == torch.float16 and q.dim() == 3, "q must be float16 [batch, heads, head_dim]")
-    assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
+    if q.dtype != torch.float16 or q.dim() != 3:
+        raise ValueError("q must be float16 [batch, heads, head_dim]")
     batch, q_heads, d = q.shape
     q_sb, q_sh, q_sd = q.stride()
-    _require(q_sd == 1, "q must be contiguous along head_dim")
-    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
-    kv_heads = k_cache.shape[1]
+    k_ptr, v_ptr, tok_stride, head_stride, pool_tokens, kv_heads, kv_d = kv
+    assert d == kv_d
     kind = _TABLE_KINDS[table_kind]
-    _require(kind in (TABLE_BLOCK, TABLE_TOKEN), "decode takes a 'token' or 'block' table")
-    _require(tbl.dtype == torch.int32 and tbl.dim() == 2 and tbl.stride(1) == 1,
-             "the table must be a 2-D int32 tensor contiguous along its last dimension")
+    if q_sd != 1 or kind == TABLE_DENSE:
+        raise ValueError("q must be contiguous along head_dim; decode takes a 'token' or 'block' table")
+    if tbl.dtype != torch.int32 or tbl.dim() != 2 or tbl.stride(1) != 1:
+        raise ValueError("the table must be a 2-D int32 tensor contiguous along its last dimension")
     tbl_rows, tbl_cols = tbl.shape
-    _require(b_seq_len.shape[0] == batch, "b_seq_len must have one entry per batch row")
-    lens_ptr, lens_i64 = _lens_arg(b_seq_len, "b_seq_len")
+    lens_dtype = b_seq_len.dtype
+    if (lens_dtype != torch.int64 and lens_dtype != torch.int32) or b_seq_len.dim() != 1 \
+            or not b_seq_len.is_contiguous() or b_seq_len.shape[0] != batch:
+        raise ValueError("b_seq_len must be a contiguous int32 or int64 tensor with one entry per batch row")
     rows_ptr = 0
     if b_req_idx is not None:
-        _require(b_req_idx.dtype == torch.int32 and b_req_idx.shape == (batch,)
-                 and b_req_idx.is_contiguous(), "b_req_idx must be contiguous int32 [batch]")
+        if b_req_idx.dtype != torch.int32 or b_req_idx.shape != (batch,) or not b_req_idx.is_contiguous():
+            raise ValueError("b_req_idx must be contiguous int32 [batch]")
         rows_ptr = b_req_idx.data_ptr()
-    else:
-        _require(tbl_rows >= batch, "the table has fewer rows than the batch")
-    width_tokens = tbl_cols * (page_size if kind == TABLE_BLOCK else 1)
+    elif tbl_rows < batch:
+        raise ValueError("the table has fewer rows than the batch")
     max_len = int(max_actual_seq_len)
-    _require(0 <= max_len <= width_tokens, "max_actual_seq_len exceeds the table width")
+    if not 0 <= max_len <= tbl_cols * (page_size if kind == TABLE_BLOCK else 1):
+        raise ValueError("max_actual_seq_len exceeds the table width")
     if out is None:
         out = torch.empty_like(q)
-    else:
-        _require(out.shape == q.shape and out.dtype == torch.float16 and out.stride(2) == 1,
-                 "out must match q")
+    elif out.shape != q.shape or out.dtype != torch.float16 or out.stride(2) != 1:
+        raise ValueError("out must match q")
     if batch == 0:
         return out
     if _DEBUG:
@@ -461,29 +478,46 @@ def _decode_call(new_rows, slots, q, k_cache, v_cache, qk_scale, tbl, b_seq_len,
     ws = decode_workspace(dev, batch, q_heads, kv_heads, d)
     flags = DECODE_SERIALIZED if metadata_fresh else 0
     lib = _lib.lib()
+    out_sb, out_sh, _ = out.stride()
     with _on_device(dev):
         if new_rows is None:
             rc = lib.b200kv_paged_decode(
-                q.data_ptr(), q_sb, q_sh,
-                k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
-                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr, lens_ptr, lens_i64,
+                q.data_ptr(), q_sb, q_sh, k_ptr, v_ptr, tok_stride, head_stride, pool_tokens,
+                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr,
+                b_seq_len.data_ptr(), lens_dtype == torch.int64,
                 batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
-                ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
+                ws.data_ptr(), ws.numel(), out.data_ptr(), out_sb, out_sh,
                 flags, status_tensor(dev).data_ptr(), _stream(dev),
             )
         else:
             rc = lib.b200kv_append_paged_decode(
                 new_rows[0], new_rows[1], new_rows[2], new_rows[3], slots.data_ptr(),
-                q.data_ptr(), q_sb, q_sh,
-                k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens,
-                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr, lens_ptr, lens_i64,
+                q.data_ptr(), q_sb, q_sh, k_ptr, v_ptr, tok_stride, head_stride, pool_tokens,
+                tbl.data_ptr(), tbl.stride(0), kind, tbl_rows, tbl_cols, rows_ptr,
+                b_seq_len.data_ptr(), lens_dtype == torch.int64,
                 batch, q_heads, kv_heads, d, int(page_size), float(qk_scale), max_len,
-                ws.data_ptr(), ws.numel(), out.data_ptr(), out.stride(0), out.stride(1),
+                ws.data_ptr(), ws.numel(), out.data_ptr(), out_sb, out_sh,
                 flags, status_tensor(dev).data_ptr(), _stream(dev),
             )
-    _lib.check(rc)
-    _after_call(dev)
+    if rc != 0:
+        _lib.check(rc)
+    if _DEBUG:
+        check_status(dev)
     return out
+
+
+def _pool_geometry(KV_Buffer: torch.Tensor):
+    """``kv`` tuple of :func:`_decode_call` for a whole pool ``[pool_tokens, 2*kv_heads, head_dim]``,
+    without materialising its K and V views."""
+    if KV_Buffer.dim() != 3 or KV_Buffer.dtype != torch.float16:
+        raise ValueError("KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
+    pool_tokens, rows, d = KV_Buffer.shape
+    s0, s1, s2 = KV_Buffer.stride()
+    if rows % 2 != 0 or s2 != 1 or s1 != d:
+        raise ValueError("KV_Buffer must hold 2*kv_heads rows per token, contiguous inside a token")
+    kvh = rows // 2
+    k_ptr = KV_Buffer.data_ptr()
+    return (k_ptr, k_ptr + kvh * d * 2, s0, s1, pool_tokens, kvh, d)
 
 
 def flash_decoding(
@@ -516,7 +550,11 @@ def flash_decoding(
     ``b_seq_len``, ``b_req_idx`` or the table were written by the kernel launched immediately
     before this call on the same stream (the launch then gives up its overlap with that kernel).
     """
-    return _decode_call(None, None, q, k_cache, v_cache, qk_scale, b_req_tokens_table, b_seq_len,
+    assert q.shape[-1] == k_cache.shape[-1] == v_cache.shape[-1]
+    tok_stride, head_stride, pool_tokens = _kv_views(k_cache, v_cache)
+    kv = (k_cache.data_ptr(), v_cache.data_ptr(), tok_stride, head_stride, pool_tokens, k_cache.shape[1],
+          k_cache.shape[2])
+    return _decode_call(None, None, q, kv, qk_scale, b_req_tokens_table, b_seq_len,
                         max_actual_seq_len, b_req_idx, table_kind, page_size, out, metadata_fresh)
 
 
@@ -543,21 +581,21 @@ def append_flash_decoding(
     ``KV_Values`` is ``[batch, 2*kv_heads, head_dim]``, ``Select_Index[b]`` the slot of sequence
     ``b``'s newest token (position ``b_seq_len[b] - 1``, the lengths already count it).  The pool
     rows are written bit-exactly; the other arguments are those of :func:`flash_decoding`."""
-    _require(KV_Buffer.dim() == 3 and KV_Buffer.dtype == torch.float16 and KV_Buffer.shape[1] % 2 == 0,
-             "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
-    rows, d = KV_Buffer.shape[1], KV_Buffer.shape[2]
+    kv = _pool_geometry(KV_Buffer)
+    kvh, d = kv[5], kv[6]
     batch = q.shape[0]
-    _require(KV_Values.dtype == torch.float16 and KV_Values.shape == (batch, rows, d)
-             and KV_Values.stride(2) == 1 and KV_Values.stride(1) == d and KV_Values.device == KV_Buffer.device,
-             "KV_Values must be float16 [batch, 2*kv_heads, head_dim] on the pool's device, contiguous inside a token")
-    _require(Select_Index.dtype == torch.int32 and Select_Index.shape == (batch,) and Select_Index.is_contiguous()
-             and Select_Index.device == KV_Buffer.device, "Select_Index must be contiguous int32 [batch]")
-    _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d, "KV_Buffer must be contiguous inside a token")
-    kvh = rows // 2
-    k_ptr, stride = KV_Values.data_ptr(), KV_Values.stride(0)
-    return _decode_call((k_ptr, k_ptr + kvh * d * 2, stride, stride), Select_Index, q, KV_Buffer[:, :kvh],
-                        KV_Buffer[:, kvh:], qk_scale, b_req_tokens_table, b_seq_len, max_actual_seq_len,
-                        b_req_idx, table_kind, page_size, out, metadata_fresh)
+    if KV_Values.dtype != torch.float16 or KV_Values.shape != (batch, 2 * kvh, d) or KV_Values.device != KV_Buffer.device:
+        raise ValueError("KV_Values must be float16 [batch, 2*kv_heads, head_dim] on the pool's device")
+    v_stride, v_s1, v_s2 = KV_Values.stride()
+    if v_s2 != 1 or v_s1 != d:
+        raise ValueError("KV_Values must be contiguous inside a token")
+    if Select_Index.dtype != torch.int32 or Select_Index.shape != (batch,) or not Select_Index.is_contiguous() \
+            or Select_Index.device != KV_Buffer.device:
+        raise ValueError("Select_Index must be contiguous int32 [batch] on the pool's device")
+    k_ptr = KV_Values.data_ptr()
+    return _decode_call((k_ptr, k_ptr + kvh * d * 2, v_stride, v_stride), Select_Index, q, kv, qk_scale,
+                        b_req_tokens_table, b_seq_len, max_actual_seq_len, b_req_idx, table_kind,
+                        page_size, out, metadata_fresh)
 
 
 def append_flash_decoding_split(
@@ -580,20 +618,20 @@ def append_flash_decoding_split(
     """:func:`append_flash_decoding` with the new K and V rows given separately
     (``[batch, kv_heads, head_dim]`` each), i.e. without ``torch.cat([xk, xv], dim=-2)``
     (``lite_llama/models/qwen3.py:62``)."""
-    _require(KV_Buffer.dim() == 3 and KV_Buffer.dtype == torch.float16 and KV_Buffer.shape[1] % 2 == 0,
-             "KV_Buffer must be [pool_tokens, 2*kv_heads, head_dim] float16")
-    kvh, d = KV_Buffer.shape[1] // 2, KV_Buffer.shape[2]
+    kv = _pool_geometry(KV_Buffer)
+    kvh, d = kv[5], kv[6]
     batch = q.shape[0]
     for t, name in ((xk, "xk"), (xv, "xv")):
-        _require(t.dtype == torch.float16 and t.shape == (batch, kvh, d) and t.stride(2) == 1 and t.stride(1) == d
-                 and t.device == KV_Buffer.device,
-                 f"{name} must be float16 [batch, kv_heads, head_dim] on the pool's device, contiguous inside a token")
-    _require(Select_Index.dtype == torch.int32 and Select_Index.shape == (batch,) and Select_Index.is_contiguous()
-             and Select_Index.device == KV_Buffer.device, "Select_Index must be contiguous int32 [batch]")
-    _require(KV_Buffer.stride(2) == 1 and KV_Buffer.stride(1) == d, "KV_Buffer must be contiguous inside a token")
-    return _decode_call((xk.data_ptr(), xv.data_ptr(), xk.stride(0), xv.stride(0)), Select_Index, q,
-                        KV_Buffer[:, :kvh], KV_Buffer[:, kvh:], qk_scale, b_req_tokens_table, b_seq_len,
-                        max_actual_seq_len, b_req_idx, table_kind, page_size, out, metadata_fresh)
+        if t.dtype != torch.float16 or t.shape != (batch, kvh, d) or t.stride(2) != 1 or t.stride(1) != d \
+                or t.device != KV_Buffer.device:
+            raise ValueError(f"{name} must be float16 [batch, kv_heads, head_dim] on the pool's device, "
+                             "contiguous inside a token")
+    if Select_Index.dtype != torch.int32 or Select_Index.shape != (batch,) or not Select_Index.is_contiguous() \
+            or Select_Index.device != KV_Buffer.device:
+        raise ValueError("Select_Index must be contiguous int32 [batch] on the pool's device")
+    return _decode_call((xk.data_ptr(), xv.data_ptr(), xk.stride(0), xv.stride(0)), Select_Index, q, kv,
+                        qk_scale, b_req_tokens_table, b_seq_len, max_actual_seq_len, b_req_idx, table_kind,
+                        page_size, out, metadata_fresh)
 
 
 def set_decode_option(option: int, value: int) -> None:

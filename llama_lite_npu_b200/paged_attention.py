@@ -254,8 +254,7 @@ class PagedReqTokensManager:
             if not dirty:
                 continue
             width = host_np.shape[1]
-            off = np.concatenate([np.arange(row * width + s, row * width + e, dtype=np.int64)
-                                  for row, s, e in dirty])
+            off = np.fromiter((row * width + t for row, s, e in dirty for t in range(s, e)), dtype=np.int64)
             kernels.patch_table(dev, off, host_np.reshape(-1)[off])
             dirty.clear()
         if self._dirty_counts:
