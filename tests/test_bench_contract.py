@@ -32,3 +32,21 @@ def test_other_ranks_of_the_reference_arm_do_nothing():
         capture_output=True, text=True, timeout=120, cwd=ROOT,
         env={**__import__("os").environ, "RANK": "1", "LOCAL_RANK": "1", "WORLD_SIZE": "2"})
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_reference_arm_covers_the_prefill_workload_with_the_same_config_echo():
+    """`--impl reference --workload c4` runs (a bounded sample of the oracle's prefill) and echoes
+    the same `config`, `steps` and `warmup` the GPU arm prints for that workload."""
+    out = subprocess.run(
+        [sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--workload", "c4", "--steps", "1",
+         "--warmup", "0"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads([ln for ln in out.stdout.splitlines() if ln.startswith("{")][0])
+    assert line["impl"] == "reference" and line["metric"] == "paged_prefill_tensor_throughput"
+    assert line["unit"] == "TFLOP/s" and line["value"] > 0 and (line["steps"], line["warmup"]) == (1, 0)
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from llama_lite_npu_b200 import workloads as W
+
+    assert line["config"] == bench.workload_config(W.C4)
+    assert "requests" in line["cpu_baseline"]["sample"]
