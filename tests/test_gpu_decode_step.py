@@ -300,3 +300,40 @@ def test_debug_mode_checks_index_tensors_on_the_host_before_launch():
     finally:
         kernels.set_debug(False)
     kernels.check_status(0)
+
+
+def test_prefill_request_outside_the_table_is_skipped_and_reported():
+    """A request id outside the table, or a context + chunk length beyond the table's width, must
+    not become a table read: that request is skipped and reported, the others are computed."""
+    c = G.build_prefill("prefill_hist_gqa2")
+    kvh = c.cfg.kv_heads
+    pool = c.pool.clone()
+    O.kv_append(c.new_kv, c.slots, pool)
+    want = O.paged_attention(c.q, pool[:, :kvh], pool[:, kvh:], SCALE, c.token_table, c.req_ids, c.q_start,
+                             c.ctx_lens_t, c.q_lens_t)
+    pool_d = pool.to(DEV)
+    args = dict(table_kind="block")
+
+    def run(req_ids, ctx):
+        return kernels.paged_chunk_flash_attention(
+            c.q.to(DEV), pool_d[:, :kvh], pool_d[:, kvh:], SCALE * 1.4426950408889634, c.block_table.to(DEV),
+            req_ids.to(DEV), c.q_start.to(DEV), ctx.to(DEV), c.q_lens_t.to(DEV), c.max_q_len, **args)
+
+    def rows(r):
+        s0 = int(c.q_start[r])
+        return slice(s0, s0 + int(c.q_lens[r]))
+
+    bad_ids = c.req_ids.clone()
+    bad_ids[1] = c.block_table.shape[0] + 3
+    got = run(bad_ids, c.ctx_lens_t)
+    with pytest.raises(RuntimeError, match="length"):
+        kernels.check_status(0)
+    for r in (0, 2):
+        assert _maxdiff(got[rows(r)], want[rows(r)]) <= ATTN_TOL
+    bad_ctx = c.ctx_lens_t.clone()
+    bad_ctx[2] = c.block_table.shape[1] * 16                      # context alone fills the table: ctx + q overflows it
+    got = run(c.req_ids, bad_ctx)
+    with pytest.raises(RuntimeError, match="length"):
+        kernels.check_status(0)
+    for r in (0, 1):
+        assert _maxdiff(got[rows(r)], want[rows(r)]) <= ATTN_TOL
