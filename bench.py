@@ -13,8 +13,9 @@ max-over-ranks reduction.
 
 Prints ONE JSON line (rank 0).  ``value`` is algorithmic HBM traffic of the whole job per
 second with all inputs resident in HBM (CUDA-graph replay, device-timed); ``e2e`` is the
-same metric through the Python operator API with the step's inputs copied from pinned host
-memory and the result copied back inside the timed region; ``check`` is the max-abs-error of
+same metric through the library's host-buffer form of the step (HostDecodeSteps): the step's
+inputs are copied from pinned host memory and the result copied back inside the timed region,
+every step; ``check`` is the max-abs-error of
 a few sequences of the benchmarked run's own output against the CPU oracle (untimed); at one
 GPU ``secondary`` carries the other benchmark configurations (30B-A3B decode, the long mixed
 decode on its full 2^20-page pool, packed prefill), timed the same way outside the headline
@@ -415,72 +416,57 @@ def decode_bench(cfg, dev, steps, warmup, timer, prologue=False, with_e2e=True):
         n_k = max(steps, GRAPH_STEPS)
         res["ms_kernel"] = timer.run(decode_only, n_k) / n_k
         if with_e2e:
-            # ---- e2e: operator API, host inputs in, result out, every step ---------------------
-            # The step's host inputs (q, the new K/V rows, slot_mapping, lengths) sit in ONE pinned
-            # staging buffer and cross PCIe in one copy; the result comes back in one copy.
-            parts = [("q", case.q), ("kv", case.new_kv), ("lens", case.seq_lens_t), ("slots", case.slots)]
-            offs, cur = {}, 0
-            for name, t in parts:
-                cur = (cur + 15) // 16 * 16
-                offs[name] = (cur, t.numel() * t.element_size())
-                cur += t.numel() * t.element_size()
-            # Two staging sets and three streams: step i+1's inputs cross PCIe while step i computes,
-            # and step i's result goes back while step i+1 computes.  Every step still makes both
-            # copies inside the timed region.
-            depth = 2
-            h_in = [torch.empty(cur, dtype=torch.uint8).pin_memory() for _ in range(depth)]
-            d_in = [torch.empty(cur, dtype=torch.uint8, device=dev) for _ in range(depth)]
-            h_out = [torch.empty(case.q.shape, dtype=case.q.dtype).pin_memory() for _ in range(depth)]
-            d_out = [torch.empty_like(case.q) for _ in range(depth)]
+            # ---- e2e: host buffers in, result out, every step ---------------------------------
+            # The library's host-buffer form of the step (HostDecodeSteps): q, the new K/V rows,
+            # slot_mapping and lengths sit in pinned staging and cross PCIe in one copy, the result
+            # comes back in one copy, one library call per step.  Three slots: step i+1's inputs
+            # travel while step i computes, step i's result returns while step i+1 computes.
+            # Every step makes both copies inside the timed region, and a slot is only reused
+            # after the host has waited for its result.
+            from llama_lite_npu_b200.host_step import HostDecodeSteps
 
-            def view(buf, name, like):
-                o, n = offs[name]
-                return buf[o:o + n].view(like.dtype).view(like.shape)
+            depth = 3
+            batch = case.q.shape[0]
+            hs = HostDecodeSteps(batch, cfg.q_heads, kvh, cfg.head_dim, depth=depth, device=torch.device(dev).index)
+            bound = [hs.bind(p, case.block_table, qk_scale=scale, table_kind="block") for p in pools]
+            new_kv_host = case.new_kv.cpu().numpy()
+            for k in range(depth):
+                buf = hs.buffers(k, batch)
+                buf.q[...] = case.q.cpu().numpy()
+                buf.new_k[...] = new_kv_host[:, :kvh]
+                buf.new_v[...] = new_kv_host[:, kvh:]
+                buf.seq_lens[...] = case.seq_lens_t.cpu().numpy()
+                buf.slots[...] = case.slots.cpu().numpy()
+            buf = hs.buffers(0, batch)
+            res["h2d"] = sum(int(a.nbytes) for a in (buf.q, buf.new_k, buf.new_v, buf.seq_lens, buf.slots))
+            res["d2h"] = int(buf.out.nbytes)
+            hs_stream = hs.stream
+            stream.synchronize()
 
-            for hb in h_in:
-                for name, t in parts:
-                    view(hb, name, t).copy_(t.cpu())
-            views = [(view(b, "q", case.q), view(b, "kv", case.new_kv), view(b, "lens", case.seq_lens_t),
-                      view(b, "slots", case.slots)) for b in d_in]
-            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-            ev_in = [torch.cuda.Event() for _ in range(depth)]      # inputs of the slot are on the device
-            ev_done = [torch.cuda.Event() for _ in range(depth)]    # the slot's kernel has finished
-            ev_out = [torch.cuda.Event() for _ in range(depth)]     # the slot's result has left the device
+            def e2e_run(n):
+                for i in range(n):
+                    k = i % depth
+                    if i >= depth:
+                        hs.wait(k)                     # the result of step i - depth is in host memory
+                    hs.submit(k, batch, bound[i % layers], case.max_len)
+                for k in range(depth):
+                    hs.wait(k)
 
-            def e2e_step(i):
-                k = i % depth
-                d_q, d_kv, d_lens, d_slots = views[k]
-                s_in.wait_event(ev_done[k])            # the kernel that last read this slot's inputs is done
-                with torch.cuda.stream(s_in):
-                    d_in[k].copy_(h_in[k], non_blocking=True)
-                    ev_in[k].record(s_in)
-                stream.wait_event(ev_in[k])
-                stream.wait_event(ev_out[k])           # the slot's previous result has been copied out
-                kernels.append_flash_decoding(d_kv, d_slots, pools[i % layers], d_q, scale, case.block_table,
-                                              d_lens, case.max_len, table_kind="block", out=d_out[k])
-                ev_done[k].record(stream)
-                s_out.wait_event(ev_done[k])
-                with torch.cuda.stream(s_out):
-                    h_out[k].copy_(d_out[k], non_blocking=True)
-                    ev_out[k].record(s_out)
-
-            def drain():
-                stream.wait_stream(s_in)
-                stream.wait_stream(s_out)
-
-            for i in range(4):
-                e2e_step(i)
-            drain()
+            e2e_run(2 * depth)
             timer.barrier()
             x0, x1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            x0.record(stream)
-            for i in range(steps):
-                e2e_step(i)
-            drain()
-            x1.record(stream)
+            x0.record(hs_stream)
+            e2e_run(steps)
+            x1.record(hs_stream)                       # after the host has the last result
+            x1.synchronize()
             timer.barrier()
             res["ms_e2e_total"] = x0.elapsed_time(x1)
-            res["h2d"], res["d2h"] = cur, h_out[0].numel() * h_out[0].element_size()
+            # the last step's result in host memory against the device-tensor path on the same pool
+            got = torch.from_numpy(hs.buffers((steps - 1) % depth, batch).out.copy())
+            step(steps - 1)
+            stream.synchronize()
+            res["e2e_check"] = float((got.float() - out.float().cpu()).abs().max())
+            hs.close()
         kernels.check_status(torch.device(dev).index)
     del pools
     return res
@@ -650,7 +636,10 @@ def run_b200(args, cfg_full):
                 "traffic": ncu_traffic(cfg_full.name, world),
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["h2d"] * world,
-                    "d2h_bytes_per_step": r["d2h"] * world, "us_per_step": ms_e2e_total / args.steps * 1e3},
+                    "d2h_bytes_per_step": r["d2h"] * world, "us_per_step": ms_e2e_total / args.steps * 1e3,
+                    "api": "HostDecodeSteps.submit / wait (b200kv_host_steps_*): pinned host buffers in and out, "
+                           "3 slots in flight",
+                    "max_abs_diff_vs_device_tensor_path": r["e2e_check"]},
             "gpu_launches": r["launches_per_step"] * args.steps,
             "check": check,
             "clocks": clocks,

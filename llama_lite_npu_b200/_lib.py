@@ -13,7 +13,7 @@ from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libb200kv.so"
 
-# name -> (restype, argtypes); mirrors include/b200kv.h and include/b200kv_prefix_cache.h one to one.
+# name -> (restype, argtypes); mirrors the headers under include/ one to one.
 _SIGNATURES = {
     "b200kv_version": (c_int, []),
     "b200kv_strerror": (c_char_p, [c_int]),
@@ -116,6 +116,20 @@ _SIGNATURES = {
     "b200kv_prefix_cache_store": (c_int64, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int64]),
     "b200kv_prefix_cache_ref_ops": (c_int64, [c_void_p, c_void_p, c_void_p, c_int64]),
     "b200kv_prefix_cache_clear": (c_int64, [c_void_p]),
+    # decode steps with host buffers (include/b200kv_host_step.h)
+    "b200kv_host_steps_create": (c_int, [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200kv_host_steps_destroy": (None, [c_void_p]),
+    "b200kv_host_steps_buffers": (
+        c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200kv_host_steps_submit": (
+        c_int,
+        [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int64, c_int64, c_int64,   # slot, batch, pool
+         c_void_p, c_int64, c_int, c_int, c_int64, c_void_p,                      # table, row ids
+         c_int, c_float, c_int64, c_int, c_void_p],
+    ),
+    "b200kv_host_steps_flush": (c_int, [c_void_p]),
+    "b200kv_host_steps_wait": (c_int, [c_void_p, c_int]),
+    "b200kv_host_steps_stream": (c_void_p, [c_void_p]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)

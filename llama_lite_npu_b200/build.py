@@ -29,6 +29,7 @@ SOURCES = (
     "tma.cu",
     "paged_prefill_sm100.cu",
     "prefix_cache.cpp",
+    "host_step.cu",
 )
 
 NVCC_FLAGS = (
