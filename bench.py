@@ -419,13 +419,13 @@ def decode_bench(cfg, dev, steps, warmup, timer, prologue=False, with_e2e=True):
             # ---- e2e: host buffers in, result out, every step ---------------------------------
             # The library's host-buffer form of the step (HostDecodeSteps): q, the new K/V rows,
             # slot_mapping and lengths sit in pinned staging and cross PCIe in one copy, the result
-            # comes back in one copy, one library call per step.  Three slots: step i+1's inputs
+            # comes back in one copy, one library call per step.  Six slots in flight: step i+1's inputs
             # travel while step i computes, step i's result returns while step i+1 computes.
             # Every step makes both copies inside the timed region, and a slot is only reused
             # after the host has waited for its result.
             from llama_lite_npu_b200.host_step import HostDecodeSteps
 
-            depth = 3
+            depth = 6
             batch = case.q.shape[0]
             hs = HostDecodeSteps(batch, cfg.q_heads, kvh, cfg.head_dim, depth=depth, device=torch.device(dev).index)
             bound = [hs.bind(p, case.block_table, qk_scale=scale, table_kind="block") for p in pools]
@@ -558,7 +558,19 @@ def gpu_setup(args):
     if world > 1:
         import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=torch.device(dev))
+        # The communication library announces its version on stdout when it starts; stdout
+        # carries the JSON line only, so that banner goes to stderr.
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device(dev))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     def barrier():
         torch.cuda.synchronize()
@@ -638,7 +650,7 @@ def run_b200(args, cfg_full):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": r["h2d"] * world,
                     "d2h_bytes_per_step": r["d2h"] * world, "us_per_step": ms_e2e_total / args.steps * 1e3,
                     "api": "HostDecodeSteps.submit / wait (b200kv_host_steps_*): pinned host buffers in and out, "
-                           "3 slots in flight",
+                           "6 slots in flight",
                     "max_abs_diff_vs_device_tensor_path": r["e2e_check"]},
             "gpu_launches": r["launches_per_step"] * args.steps,
             "check": check,
