@@ -416,7 +416,7 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
   float* merge_o = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [4][128][ROWS]
   float* merge_ml = merge_o + kConsumerWarps * kD * ROWS;                  // [4][ROWS][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(merge_ml + kConsumerWarps * ROWS * 2);
-  int* verdict = reinterpret_cast<int*>(bars + 2 * STAGES);  // [2]: pieces to merge (0 = not last), first team
+  int* arrival = reinterpret_cast<int*>(bars + 2 * STAGES);  // [2]: pieces to merge (0 = not last), first team
   int* scan = reinterpret_cast<int*>(merge_o);  // start-up only: [kScanThreads + 1] page prefix
 
   const int tid = threadIdx.x;
@@ -899,14 +899,14 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
           const int npieces = t_last - t_first + 1;
           const unsigned old = atomicInc(p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head,
                                          static_cast<unsigned>(npieces - 1));
-          verdict[0] = (old == static_cast<unsigned>(npieces - 1)) ? npieces : 0;
-          verdict[1] = t_first;
+          arrival[0] = (old == static_cast<unsigned>(npieces - 1)) ? npieces : 0;
+          arrival[1] = t_first;
         }
         consumer_bar();
-        const int npieces = verdict[0];
+        const int npieces = arrival[0];
         if (npieces > 0) {
           __threadfence();
-          merge_pieces<ROWS>(p, t.b, head, verdict[1], npieces, tid, merge_o, merge_ml);
+          merge_pieces<ROWS>(p, t.b, head, arrival[1], npieces, tid, merge_o, merge_ml);
         }
       }
     }
