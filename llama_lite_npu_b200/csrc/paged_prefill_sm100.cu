@@ -51,6 +51,7 @@ namespace {
 constexpr int kD = 128;
 constexpr int kPS = 16;
 constexpr int kBM = 128;             // query rows per tile
+constexpr int kQBoxRows = 16;        // query rows per TMA box: 8 boxes per head_dim half of a tile, one per lane
 constexpr int kBN = 128;             // keys per pipeline tile
 constexpr int kTilePages = kBN / kPS;
 constexpr int kSlots = 3;            // 32 KB ring slots shared by K and V tiles
@@ -342,17 +343,17 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
         set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
         break;
       }
-      if (lane == 0) {
-        mbar_arrive_expect_tx(bar_q, (active1 ? 2 : 1) * kQBytes);
-        // Rows past this request's q_len are the next request's rows (or zero fill past the end);
-        // their results are never stored.
-        const int qt = static_cast<int>(wk.q_tok0);
-        tma_load_3d(sm_q, &qmap, bar_q, 0, head0, qt, policy);
-        tma_load_3d(sm_q + kQBytes / 2, &qmap, bar_q, 64, head0, qt, policy);
-        if (active1) {
-          tma_load_3d(sm_q + kQBytes, &qmap, bar_q, 0, head0 + 1, qt, policy);
-          tma_load_3d(sm_q + kQBytes + kQBytes / 2, &qmap, bar_q, 64, head0 + 1, qt, policy);
-        }
+      if (lane == 0) mbar_arrive_expect_tx(bar_q, (active1 ? 2 : 1) * kQBytes);
+      __syncwarp();
+      {
+        // A query tile's rows are a whole token row apart in memory, so a box is 16 rows and every
+        // lane issues one: lane = 16 * head of the pair + 8 * head_dim half + row group.  Rows past
+        // this request's q_len are the next request's rows (or zero fill past the end); their
+        // results are never stored.
+        const int qh = lane >> 4, qhalf = (lane >> 3) & 1, qg = lane & 7;
+        if (qh == 0 || active1)
+          tma_load_3d(sm_q + qh * kQBytes + qhalf * (kQBytes / 2) + qg * (kQBoxRows * 128), &qmap, bar_q,
+                      qhalf * 64, head0 + qh, static_cast<int>(wk.q_tok0) + qg * kQBoxRows, policy);
       }
       // Raw table entry of this lane's page of a tile (0 when the page does not exist).
       auto fetch_id = [&](int j) -> int32_t {
@@ -711,10 +712,10 @@ paged_prefill_kernel(PrefillParams p, const __grid_constant__ CUtensorMap qmap,
 }
 
 // Tensor map over packed Q: element (d, head, token) at q + token*stride_t + head*stride_h + d;
-// box = 64 halves x 1 head x 128 tokens (one half of a query tile), 128-byte swizzle.
+// box = 64 halves x 1 head x 16 tokens (an eighth of one half of a query tile), 128-byte swizzle.
 int encode_q_tensor_map(CUtensorMap* out, const void* q, int64_t total_q, int64_t stride_t,
                         int64_t stride_h, int heads) {
-  return cached_kv_tensor_map(out, q, total_q, stride_t, stride_h, heads, kD, kBM);
+  return cached_kv_tensor_map(out, q, total_q, stride_t, stride_h, heads, kD, kQBoxRows);
 }
 
 }  // namespace
