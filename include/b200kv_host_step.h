@@ -75,6 +75,19 @@ int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, voi
                              int page_size, float scale, int64_t max_seq_len, int flags,
                              int32_t* status);
 
+/*
+ * The same with the resident state registered once: bind() remembers a pool / table / row-id /
+ * page-size / scale set and returns its index (>= 0; a negated B200KV_E* code on error), and
+ * submit_bound() names it.  A serving loop binds each layer's pool once and then passes seven
+ * scalars per step.  Bindings live as long as the handle; the memory they name must too.
+ */
+int b200kv_host_steps_bind(void* steps, void* k_base, void* v_base, int64_t kv_tok_stride,
+                           int64_t kv_head_stride, int64_t pool_tokens, const int32_t* table,
+                           int64_t table_row_stride, int table_kind, int table_rows, int64_t table_cols,
+                           const int32_t* row_ids, int page_size, float scale);
+int b200kv_host_steps_submit_bound(void* steps, int slot, int batch, int binding, int64_t max_seq_len,
+                                   int flags, int32_t* status);
+
 /* Launch the step that the last submit left pending, if any (wait() on its slot does the same). */
 int b200kv_host_steps_flush(void* steps);
 

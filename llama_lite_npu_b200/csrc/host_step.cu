@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 
 #include <new>
+#include <vector>
 
 #include "b200kv.h"
 #include "b200kv_host_step.h"
@@ -43,9 +44,25 @@ struct Slot {
   cudaEvent_t out_done = nullptr;   // the slot's result is in h_out
   DecodeArgs args{};                // of the slot's submitted step
   size_t out_bytes = 0;
+  bool idle = true;                 // no step of this slot can still be in flight (never used, or waited for)
+};
+
+// The resident state a step runs on (pool, table, row ids, scale), registered once.
+struct Binding {
+  void* k_base;
+  void* v_base;
+  int64_t kv_tok_stride, kv_head_stride, pool_tokens;
+  const int32_t* table;
+  int64_t table_row_stride;
+  int table_kind, table_rows;
+  int64_t table_cols;
+  const int32_t* row_ids;
+  int page_size;
+  float scale;
 };
 
 struct HostSteps {
+  std::vector<Binding> bindings;
   int device = -1;
   int depth = 0;
   int max_batch = 0, q_heads = 0, kv_heads = 0, head_dim = 0;
@@ -124,7 +141,8 @@ int launch_pending(HostSteps& h) {
   h.pending = -1;
   // after its inputs have landed and after the slot's previous result has left d_out
   HS_TRY(wait_unless_done(h.s_run, s.in_done));
-  HS_TRY(wait_unless_done(h.s_run, s.out_done));
+  if (!s.idle) HS_TRY(wait_unless_done(h.s_run, s.out_done));
+  s.idle = false;
   const int rc = paged_decode(s.args, h.s_run);
   if (rc != B200KV_OK) return rc;
   HS_TRY(cudaEventRecord(s.step_done, h.s_run));
@@ -190,15 +208,15 @@ int b200kv_host_steps_buffers(void* steps, int slot, int batch, void** q, void**
   return B200KV_OK;
 }
 
-int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, void* v_base,
-                             int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
-                             const int32_t* table, int64_t table_row_stride, int table_kind,
-                             int table_rows, int64_t table_cols, const int32_t* row_ids, int page_size,
-                             float scale, int64_t max_seq_len, int flags, int32_t* status) {
-  using namespace b200kv;
-  HostSteps* h = handle(steps, slot);
-  if (h == nullptr || batch < 1 || batch > h->max_batch) return B200KV_EINVAL;
-  if (k_base == nullptr || v_base == nullptr || table == nullptr || status == nullptr) return B200KV_EINVAL;
+}  // extern "C"
+
+namespace b200kv {
+namespace {
+
+int submit_step(HostSteps* h, int slot, int batch, const Binding& bd, int64_t max_seq_len, int flags,
+                int32_t* status) {
+  if (batch < 1 || batch > h->max_batch) return B200KV_EINVAL;
+  if (bd.k_base == nullptr || bd.v_base == nullptr || bd.table == nullptr || status == nullptr) return B200KV_EINVAL;
   if (h->pending == slot) return B200KV_EINVAL;   // the slot's previous step has not even been launched
   int dev = -1;
   HS_TRY(cudaGetDevice(&dev));
@@ -206,8 +224,9 @@ int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, voi
   const Layout l = layout_for(batch, h->q_heads, h->kv_heads, h->head_dim);
   Slot& s = h->slot[slot];
 
-  // Inputs first: the staging on the device is free once the kernel that last read it has finished.
-  HS_TRY(wait_unless_done(h->s_in, s.step_done));
+  // Inputs first: the staging on the device is free once the kernel that last read it has finished
+  // (known without asking when the host has already waited for the slot's result).
+  if (!s.idle) HS_TRY(wait_unless_done(h->s_in, s.step_done));
   HS_TRY(cudaMemcpyAsync(s.d_in, s.h_in, l.in_bytes, cudaMemcpyHostToDevice, h->s_in));
   HS_TRY(cudaEventRecord(s.in_done, h->s_in));
 
@@ -223,17 +242,17 @@ int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, voi
   a.q = s.d_in + l.q;
   a.q_stride_b = q_row;
   a.q_stride_h = h->head_dim;
-  a.k_base = k_base;
-  a.v_base = v_base;
-  a.kv_tok_stride = kv_tok_stride;
-  a.kv_head_stride = kv_head_stride;
-  a.pool_tokens = pool_tokens;
-  a.table = table;
-  a.table_row_stride = table_row_stride;
-  a.table_kind = table_kind;
-  a.table_rows = table_rows;
-  a.table_cols = table_cols;
-  a.row_ids = row_ids;
+  a.k_base = bd.k_base;
+  a.v_base = bd.v_base;
+  a.kv_tok_stride = bd.kv_tok_stride;
+  a.kv_head_stride = bd.kv_head_stride;
+  a.pool_tokens = bd.pool_tokens;
+  a.table = bd.table;
+  a.table_row_stride = bd.table_row_stride;
+  a.table_kind = bd.table_kind;
+  a.table_rows = bd.table_rows;
+  a.table_cols = bd.table_cols;
+  a.row_ids = bd.row_ids;
   a.seq_lens = s.d_in + l.lens;
   a.seq_lens_i64 = 0;
   a.new_k = s.d_in + l.new_k;
@@ -245,8 +264,8 @@ int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, voi
   a.q_heads = h->q_heads;
   a.kv_heads = h->kv_heads;
   a.head_dim = h->head_dim;
-  a.page_size = page_size;
-  a.scale = scale;
+  a.page_size = bd.page_size;
+  a.scale = bd.scale;
   a.max_seq_len = max_seq_len;
   a.workspace = h->workspace;
   a.workspace_bytes = h->workspace_bytes;
@@ -259,6 +278,45 @@ int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, voi
   h->pending = slot;
   if (h->depth == 1) return launch_pending(*h);   // nothing to overlap with
   return B200KV_OK;
+}
+
+}  // namespace
+}  // namespace b200kv
+
+extern "C" {
+
+int b200kv_host_steps_submit(void* steps, int slot, int batch, void* k_base, void* v_base,
+                             int64_t kv_tok_stride, int64_t kv_head_stride, int64_t pool_tokens,
+                             const int32_t* table, int64_t table_row_stride, int table_kind,
+                             int table_rows, int64_t table_cols, const int32_t* row_ids, int page_size,
+                             float scale, int64_t max_seq_len, int flags, int32_t* status) {
+  using namespace b200kv;
+  HostSteps* h = handle(steps, slot);
+  if (h == nullptr) return B200KV_EINVAL;
+  const Binding bd{k_base,     v_base,     kv_tok_stride, kv_head_stride, pool_tokens, table, table_row_stride,
+                   table_kind, table_rows, table_cols,    row_ids,        page_size,   scale};
+  return submit_step(h, slot, batch, bd, max_seq_len, flags, status);
+}
+
+int b200kv_host_steps_bind(void* steps, void* k_base, void* v_base, int64_t kv_tok_stride,
+                           int64_t kv_head_stride, int64_t pool_tokens, const int32_t* table,
+                           int64_t table_row_stride, int table_kind, int table_rows, int64_t table_cols,
+                           const int32_t* row_ids, int page_size, float scale) {
+  using namespace b200kv;
+  HostSteps* h = static_cast<HostSteps*>(steps);
+  if (h == nullptr || k_base == nullptr || v_base == nullptr || table == nullptr) return -B200KV_EINVAL;
+  if (h->bindings.size() >= 65536) return -B200KV_ETOOLARGE;
+  h->bindings.push_back(Binding{k_base, v_base, kv_tok_stride, kv_head_stride, pool_tokens, table,
+                                table_row_stride, table_kind, table_rows, table_cols, row_ids, page_size, scale});
+  return static_cast<int>(h->bindings.size()) - 1;
+}
+
+int b200kv_host_steps_submit_bound(void* steps, int slot, int batch, int binding, int64_t max_seq_len,
+                                   int flags, int32_t* status) {
+  using namespace b200kv;
+  HostSteps* h = handle(steps, slot);
+  if (h == nullptr || binding < 0 || binding >= static_cast<int>(h->bindings.size())) return B200KV_EINVAL;
+  return submit_step(h, slot, batch, h->bindings[binding], max_seq_len, flags, status);
 }
 
 int b200kv_host_steps_flush(void* steps) {
@@ -277,6 +335,7 @@ int b200kv_host_steps_wait(void* steps, int slot) {
     if (rc != B200KV_OK) return rc;
   }
   HS_TRY(cudaEventSynchronize(h->slot[slot].out_done));
+  h->slot[slot].idle = true;
   return B200KV_OK;
 }
 

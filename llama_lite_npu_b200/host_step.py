@@ -33,7 +33,7 @@ from .kernels import (DECODE_SERIALIZED, _TABLE_KINDS, TABLE_BLOCK, TABLE_DENSE,
                       status_tensor)
 
 HostStepBuffers = namedtuple("HostStepBuffers", "q new_k new_v seq_lens slots out")
-BoundPool = namedtuple("BoundPool", "args width keep")
+BoundPool = namedtuple("BoundPool", "index rows width keep")
 
 
 def _view(ptr: int, shape, dtype) -> np.ndarray:
@@ -58,7 +58,9 @@ class HostDecodeSteps:
         self._handle = handle
         self._status = status_tensor(self.device)
         self._views: dict[tuple[int, int], HostStepBuffers] = {}
-        self._submit = self._lib.b200kv_host_steps_submit
+        self._status_ptr = self._status.data_ptr()
+        self._bound: list = []            # keeps bound tensors alive as long as the handle
+        self._submit = self._lib.b200kv_host_steps_submit_bound
         self._wait = self._lib.b200kv_host_steps_wait
 
     # ------------------------------------------------------------------ staging
@@ -102,10 +104,17 @@ class HostDecodeSteps:
                 raise ValueError("b_req_idx must be a contiguous int32 device tensor")
             rows_ptr = b_req_idx.data_ptr()
         rows, cols = table.shape
-        args = (k_ptr, v_ptr, tok_stride, head_stride, pool_tokens, table.data_ptr(), table.stride(0), kind,
-                rows, cols, rows_ptr, int(page_size), float(qk_scale))
+        index = self._lib.b200kv_host_steps_bind(self._handle, k_ptr, v_ptr, tok_stride, head_stride, pool_tokens,
+                                                 table.data_ptr(), table.stride(0), kind, rows, cols, rows_ptr,
+                                                 int(page_size), float(qk_scale))
+        if index < 0:
+            _lib.check(-index)
         width = cols * (int(page_size) if kind == TABLE_BLOCK else 1)
-        return BoundPool(args, width, (KV_Buffer, table, b_req_idx, None if b_req_idx is None else b_req_idx.shape[0]))
+        # the tensors are kept alive with the binding: the library holds their addresses
+        bound = BoundPool(index, rows, width,
+                          (KV_Buffer, table, b_req_idx, None if b_req_idx is None else b_req_idx.shape[0]))
+        self._bound.append(bound)
+        return bound
 
     # ------------------------------------------------------------------ steps
     def submit(self, slot: int, batch: int, bound: BoundPool, max_actual_seq_len: int, *,
@@ -118,12 +127,12 @@ class HostDecodeSteps:
             raise ValueError("max_actual_seq_len exceeds the table width")
         n_rows = bound.keep[3]
         if n_rows is None:
-            if bound.args[8] < batch:
+            if bound.rows < batch:
                 raise ValueError("the table has fewer rows than the batch")
         elif n_rows != batch:
             raise ValueError("b_req_idx must have one entry per batch row")
-        rc = self._submit(self._handle, slot, batch, *bound.args, max_len,
-                          DECODE_SERIALIZED if metadata_fresh else 0, self._status.data_ptr())
+        rc = self._submit(self._handle, slot, batch, bound.index, max_len,
+                          DECODE_SERIALIZED if metadata_fresh else 0, self._status_ptr)
         if rc != 0:
             _lib.check(rc)
 
@@ -149,7 +158,8 @@ class HostDecodeSteps:
     def close(self) -> None:
         if self._handle is not None and self._handle.value:
             self._views.clear()
-            self._lib.b200kv_host_steps_destroy(self._handle)
+            self._lib.b200kv_host_steps_destroy(self._handle)   # waits for the steps in flight
+            self._bound.clear()
             self._handle = None
 
     def __del__(self):

@@ -160,3 +160,35 @@ def test_host_steps_argument_checks():
         steps.bind(pool.cpu(), tbl, qk_scale=SCALE)     # the pool is device state
     steps.close()
     steps.close()                                       # idempotent
+
+
+def test_unbound_submit_entry_point():
+    """b200kv_host_steps_submit (every argument per call) gives what the bound form gives."""
+    c = G.build_decode("decode_gqa8_small")
+    batch, kvh = c.q.shape[0], c.cfg.kv_heads
+    want_pool, want = _oracle(c)
+    steps = HostDecodeSteps(batch, c.cfg.q_heads, kvh, 128, depth=2)
+    pool = c.pool.to(DEV)
+    tbl = c.block_table.to(DEV)
+    torch.cuda.synchronize()
+    _fill(steps.buffers(0, batch), c)
+    k_ptr, v_ptr, tok_stride, head_stride, pool_tokens, _, _ = kernels._pool_geometry(pool)
+    rc = steps._lib.b200kv_host_steps_submit(
+        steps._handle, 0, batch, k_ptr, v_ptr, tok_stride, head_stride, pool_tokens, tbl.data_ptr(), tbl.stride(0),
+        kernels.TABLE_BLOCK, tbl.shape[0], tbl.shape[1], None, 16, SCALE, c.max_len, 0,
+        kernels.status_tensor(0).data_ptr())
+    assert rc == 0
+    steps.flush()
+    steps.wait(0)
+    kernels.check_status(0)
+    assert torch.equal(pool.cpu(), want_pool)
+    got = torch.from_numpy(steps.buffers(0, batch).out.copy())
+    assert float((got.float() - want.float()).abs().max()) <= ATTN_TOL
+    # a slot whose step is still pending cannot take another one
+    _fill(steps.buffers(1, batch), c)
+    bound = steps.bind(pool, tbl, qk_scale=SCALE, table_kind="block")
+    steps.submit(1, batch, bound, c.max_len)
+    with pytest.raises(ValueError):
+        steps.submit(1, batch, bound, c.max_len)
+    steps.wait(1)
+    steps.close()
