@@ -326,9 +326,14 @@ __device__ __forceinline__ void merge_pieces(const DecodeParams& p, int b, int h
   auto load_batch = [&](float (&ov)[kMergeBatch][8], int r0, int p0) {
 #pragma unroll
     for (int j = 0; j < kMergeBatch; ++j) {
-      const int64_t slot = slot_of(min(p0 + j, npieces - 1));
+      if (p0 + j < npieces) {   // the same for every thread of the CTA
+        const int64_t slot = slot_of(p0 + j);
 #pragma unroll
-      for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
+        for (int r = 0; r < 8; ++r) ov[j][r] = __ldcg(p.part_o + (slot * ROWS + r0 + r) * kD + tid);
+      } else {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) ov[j][r] = 0.f;
+      }
     }
   };
   // The first batch of partial outputs needs no weights to be requested: its loads are issued
@@ -899,15 +904,17 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
           const int npieces = t_last - t_first + 1;
           const unsigned old = atomicInc(p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head,
                                          static_cast<unsigned>(npieces - 1));
-          arrival[0] = (old == static_cast<unsigned>(npieces - 1)) ? npieces : 0;
+          const bool last_arrival = old == static_cast<unsigned>(npieces - 1);
+          arrival[0] = last_arrival ? npieces : 0;
           arrival[1] = t_first;
+          // Acquire side of the hand-over, paid by the merging CTA only: this thread saw the other
+          // pieces' counts; the fence orders their published rows before everything that follows,
+          // and the named barrier below extends that to the other 127 threads.
+          if (last_arrival) __threadfence();
         }
         consumer_bar();
         const int npieces = arrival[0];
-        if (npieces > 0) {
-          __threadfence();
-          merge_pieces<ROWS>(p, t.b, head, arrival[1], npieces, tid, merge_o, merge_ml);
-        }
+        if (npieces > 0) merge_pieces<ROWS>(p, t.b, head, arrival[1], npieces, tid, merge_o, merge_ml);
       }
     }
   }
