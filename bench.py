@@ -18,8 +18,8 @@ inputs are copied from pinned host memory and the result copied back inside the 
 every step; ``check`` is the max-abs-error of
 a few sequences of the benchmarked run's own output against the CPU oracle (untimed); at one
 GPU ``secondary`` carries the other benchmark configurations (30B-A3B decode, the long mixed
-decode on its full 2^20-page pool, packed prefill), timed the same way outside the headline
-region.  ``--impl reference`` times the CPU torch statement of the same path (the oracle port)
+decode on its full 2^20-page pool, packed prefill) and the stand-alone KV append at a
+prefill-sized token count, timed the same way outside the headline region.  ``--impl reference`` times the CPU torch statement of the same path (the oracle port)
 on the host cores instead.
 """
 
@@ -601,7 +601,43 @@ def secondary_lines(dev, timer, sampler, peaks):
     out["c4"] = {"workload": W.C4.name, "us": r["ms_kernel"] * 1e3, "us_per_step": r["ms_step"] * 1e3,
                  "achieved": ach, "unit": "TFLOP/s", "frac": ach / peaks["tensor"], "bound": "tensor",
                  "flops_per_launch": r["flops"], "check": r["check"], "clocks": sampler.summary(reset=True)}
+    del r
+    torch.cuda.empty_cache()
+    with sampler:
+        out["append"] = append_bench(dev, timer, peaks)
+    out["append"]["clocks"] = sampler.summary(reset=True)
     return out
+
+
+def append_bench(dev, timer, peaks, tokens=65536, kv_heads=8, steps=20):
+    """The stand-alone KV append at a prefill-sized token count (the decode step's one-token
+    append rides in the decode launch): scatter `tokens` rows of 2*kv_heads*128 fp16 into a pool
+    twice as large by a seeded permutation; two pools alternate so no launch finds its rows in L2."""
+    from llama_lite_npu_b200 import kernels
+
+    rows = 2 * kv_heads
+    g = torch.Generator(device=dev)
+    g.manual_seed(4242)
+    src = torch.randn(tokens, rows, 128, device=dev, dtype=torch.float16, generator=g)
+    slots = torch.randperm(2 * tokens, device=dev, generator=g)[:tokens].to(torch.int32)
+    pools = [torch.zeros(2 * tokens, rows, 128, device=dev, dtype=torch.float16) for _ in range(2)]
+    torch.cuda.synchronize()
+
+    def step(i):
+        kernels.update_kv_buffer(src, slots, pools[i % 2])
+
+    with torch.cuda.stream(timer.stream):
+        for i in range(3):
+            step(i)
+        timer.stream.synchronize()
+        kernels.check_status(torch.device(dev).index)
+        ms = timer.run(step, steps) / steps
+        exact = all(bool(torch.equal(p[slots.long()], src)) for p in pools)
+    nbytes = 2 * src.numel() * 2 + 4 * tokens
+    ach = nbytes / (ms * 1e-3) / 1e9
+    return {"workload": f"kv_append_{tokens}_tokens_{rows}x128_fp16", "us": ms * 1e3, "achieved": ach, "unit": "GB/s",
+            "frac": ach / peaks["hbm"], "bound": "hbm", "bytes_per_launch": nbytes,
+            "check": {"bit_exact": exact, "ok": exact, "against": "the rows gathered back from the pool"}}
 
 
 def run_b200(args, cfg_full):
@@ -737,12 +773,32 @@ def run_prefill(args, cfg_full):
         dist.destroy_process_group()
 
 
+def run_append(args):
+    """``--workload append``: the stand-alone KV append alone (one GPU), for profiling it."""
+    rank, local_rank, world, dev, dist, barrier = gpu_setup(args)
+    timer = Timer(torch.cuda.Stream(), barrier)
+    peaks = measured_peaks()
+    with ClockSampler(local_rank) as sampler:
+        line = append_bench(dev, timer, peaks, steps=max(args.steps, 1))
+    line = {"metric": "kv_append_hbm_throughput", "value": line["achieved"], "unit": "GB/s", "n_gpus": 1,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": line["us"] * 1e-3, "higher_is_better": True,
+            "dtype": "f16", "data": "synthetic", "config": {"workload": line["workload"]},
+            "roofline": {"bound": "hbm", "achieved": line["achieved"], "peak": peaks["hbm"], "unit": "GB/s",
+                         "frac": line["frac"], "peak_source": f"of {peaks['kind']}", "kernel": "kv_append_kernel",
+                         "us_per_launch": line["us"], "bytes_per_launch": line["bytes_per_launch"],
+                         "traffic": ncu_traffic(line["workload"], 1)},
+            "gpu_launches": args.steps, "check": line["check"], "clocks": sampler.summary()}
+    if rank == 0:
+        print(json.dumps(line))
+    sampler.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["append"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-secondary", action="store_true",
@@ -751,6 +807,9 @@ def main():
                     help="decode workloads: start each step from raw projections (fused QK-RMSNorm + "
                          "rotary embedding + KV append) instead of the append fused into the decode launch")
     args = ap.parse_args()
+    if args.workload == "append":
+        run_append(args)
+        return
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, cfg)

@@ -2,8 +2,8 @@
 //
 // Device work of update_kv_buffer in the reference
 // (lite_llama/kernels/update_kv_buffer.py:7-43): pool[slots[i]] = kv_values[i].
-// A token row is n_rows*head_dim halves (4 KB for 8 KV heads of 128); it is moved
-// as 16-byte vectors, consecutive threads on consecutive vectors of one token, so
+// A token row is n_rows*head_dim halves (4 KB for 8 KV heads of 128); a warp moves one row
+// as 16-byte vectors, consecutive lanes on consecutive vectors, eight loads in flight per lane, so
 // both the read and the write are fully coalesced 128-byte lines.  HBM-bound copy:
 // algorithmic bytes = 2 * n_tokens * row_bytes + 4 * n_tokens.
 #include "common.cuh"
@@ -14,7 +14,7 @@ namespace b200kv {
 namespace {
 
 constexpr int kAppendThreads = 256;
-constexpr int kAppendUnroll = 4;
+constexpr int kAppendUnroll = 8;
 
 struct AppendParams {
   const uint4* src0;       // combined [n, rows, d] or K [n, kvh, d]
@@ -36,34 +36,33 @@ __global__ void __launch_bounds__(kAppendThreads) kv_append_kernel(AppendParams 
   // for the previous kernel first and only then lets its own dependent start its prologue.
   cudaGridDependencySynchronize();
   cudaTriggerProgrammaticLaunchCompletion();
-  const int64_t total = p.n_tokens * p.vec_per_token;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * kAppendThreads;
-  int64_t i = static_cast<int64_t>(blockIdx.x) * kAppendThreads + threadIdx.x;
-  // Each thread keeps kAppendUnroll independent 16-byte loads in flight before storing.
-  for (; i < total; i += stride * kAppendUnroll) {
-    uint4 v[kAppendUnroll];
-    int64_t dst[kAppendUnroll];
+  // One warp per token row: 32 lanes x kAppendUnroll independent 16-byte loads cover 4 KB (a row
+  // of 8 KV heads) in one round trip; the slot is read in parallel with the row, not before it.
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = static_cast<int64_t>(gridDim.x) * (kAppendThreads / 32);
+  int64_t tok = static_cast<int64_t>(blockIdx.x) * (kAppendThreads / 32) + (threadIdx.x >> 5);
+  for (; tok < p.n_tokens; tok += warps) {
+    const int64_t slot = __ldg(p.slots + tok);
+    const bool slot_ok = slot >= 0 && slot < p.pool_tokens;
+    if (!slot_ok && lane == 0) set_status(p.status, B200KV_DEV_BAD_SLOT);
+    const uint4* s0 = p.src0 + tok * p.src0_tok_vec;
+    // V half of a split source, indexed by the row's vector number (never used when not split)
+    const uint4* s1 = p.src1 ? p.src1 + tok * p.src1_tok_vec - p.vec_split : s0;
+    uint4* dst = p.pool + (slot_ok ? slot : 0) * p.pool_tok_vec;
+    for (int c0 = 0; c0 < p.vec_per_token; c0 += 32 * kAppendUnroll) {
+      uint4 v[kAppendUnroll];
 #pragma unroll
-    for (int u = 0; u < kAppendUnroll; ++u) {
-      const int64_t j = i + u * stride;
-      dst[u] = -1;
-      if (j < total) {
-        const int64_t tok = j / p.vec_per_token;
-        const int c = static_cast<int>(j - tok * p.vec_per_token);
-        const int64_t slot = __ldg(p.slots + tok);
-        if (slot < 0 || slot >= p.pool_tokens) {
-          set_status(p.status, B200KV_DEV_BAD_SLOT);
-        } else {
-          const uint4* s = (c < p.vec_split) ? p.src0 + tok * p.src0_tok_vec + c
-                                             : p.src1 + tok * p.src1_tok_vec + (c - p.vec_split);
-          v[u] = __ldg(s);
-          dst[u] = slot * p.pool_tok_vec + c;
+      for (int u = 0; u < kAppendUnroll; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < p.vec_per_token) v[u] = __ldg(c < p.vec_split ? s0 + c : s1 + c);
+      }
+      if (slot_ok) {
+#pragma unroll
+        for (int u = 0; u < kAppendUnroll; ++u) {
+          const int c = c0 + u * 32 + lane;
+          if (c < p.vec_per_token) dst[c] = v[u];
         }
       }
-    }
-#pragma unroll
-    for (int u = 0; u < kAppendUnroll; ++u) {
-      if (dst[u] >= 0) p.pool[dst[u]] = v[u];
     }
   }
 }
@@ -72,10 +71,9 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 int launch_append(AppendParams p, cudaStream_t stream) {
   if (p.n_tokens == 0) return B200KV_OK;
-  const int64_t total = p.n_tokens * p.vec_per_token;
   const int sms = device_sm_count();
   if (sms <= 0) return B200KV_ECUDA;
-  int64_t blocks = (total + kAppendThreads * kAppendUnroll - 1) / (kAppendThreads * kAppendUnroll);
+  int64_t blocks = (p.n_tokens + kAppendThreads / 32 - 1) / (kAppendThreads / 32);   // a warp per token
   const int64_t cap = static_cast<int64_t>(sms) * 8;  // 8 resident CTAs of 256 threads per SM
   if (blocks > cap) blocks = cap;
   cudaLaunchAttribute attr[1];
