@@ -88,7 +88,8 @@ int b200kv_host_steps_bind(void* steps, void* k_base, void* v_base, int64_t kv_t
 int b200kv_host_steps_submit_bound(void* steps, int slot, int batch, int binding, int64_t max_seq_len,
                                    int flags, int32_t* status);
 
-/* Launch the step that the last submit left pending, if any (wait() on its slot does the same). */
+/* Launch the step that the last submit left pending, if any (wait() does the same for its own slot, and for
+ * another slot's step once that step's inputs have landed). */
 int b200kv_host_steps_flush(void* steps);
 
 /* Block until the slot's last submitted step has delivered its output to the host buffer. */

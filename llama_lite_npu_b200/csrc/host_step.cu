@@ -330,7 +330,11 @@ int b200kv_host_steps_wait(void* steps, int slot) {
   using namespace b200kv;
   HostSteps* h = handle(steps, slot);
   if (h == nullptr) return B200KV_EINVAL;
-  if (h->pending == slot) {
+  // A host that blocks here is not about to submit.  The pending step goes out now if it is this
+  // slot's own (it must), or if its inputs have already landed (then its launch needs no
+  // cross-stream wait and nothing is gained by holding it back).
+  if (h->pending >= 0 &&
+      (h->pending == slot || cudaEventQuery(h->slot[h->pending].in_done) == cudaSuccess)) {
     const int rc = launch_pending(*h);
     if (rc != B200KV_OK) return rc;
   }

@@ -138,7 +138,8 @@ class HostDecodeSteps:
 
     def flush(self) -> None:
         """Launch the step the last :meth:`submit` left pending (with more than one slot a step's
-        kernel is launched by the next ``submit``, by ``flush`` or by ``wait`` on its slot)."""
+        kernel is launched by the next ``submit``, by ``flush``, by ``wait`` on its slot, or by any ``wait``
+        once its inputs have landed)."""
         rc = self._lib.b200kv_host_steps_flush(self._handle)
         if rc != 0:
             _lib.check(rc)
