@@ -44,6 +44,8 @@
 // keeps walking its tiles without computing, so it still meets the other warps at every named
 // barrier and the arrival counters end at zero.
 // The kernel is HBM-bound: algorithmic bytes per token per KV head = 2 (K,V) * 128 * 2 B.
+#include <climits>
+
 #include "common.cuh"
 #include "launch.h"
 #include "tma.h"
@@ -451,21 +453,41 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
   // sequences of [t*per, (t+1)*per); scans over the 128 sums give the totals and the chunk holding
   // a boundary, then a short linear walk finds the sequence.
   int* scan_k = scan + kScanThreads + 1;   // non-empty sequences, same indexing
+  int* scan_lo = scan_k + kScanThreads + 1;  // fewest / most pages of a non-empty sequence per thread,
+  int* scan_hi = scan_lo + kScanThreads + 1; // reduced into entry [0]
   const int per = (p.batch + kScanThreads - 1) / kScanThreads;
   if (tid < kScanThreads) {
-    int sum = 0, cnt = 0;
+    int sum = 0, cnt = 0, lo_np = INT_MAX, hi_np = 0;
     const int lo = tid * per;
     const int hi = min(p.batch, lo + per);
     for (int b = lo; b < hi; ++b) {
       const int np = pages_of(seq_len_checked(p, b));
       sum += np + (np > 0 ? p.piece_cost : 0);
       cnt += np > 0;
+      if (np > 0) {
+        lo_np = min(lo_np, np);
+        hi_np = max(hi_np, np);
+      }
     }
     scan[tid + 1] = sum;
     scan_k[tid + 1] = cnt;
+    scan_lo[tid + 1] = lo_np;
+    scan_hi[tid + 1] = hi_np;
     if (tid == 0) scan[0] = scan_k[0] = 0;
   }
   __syncthreads();
+  if (warp == 2 || warp == 3) {  // fewest / most pages over the 128 entries
+    int* arr = warp == 2 ? scan_lo : scan_hi;
+    int v = arr[1 + lane * 4];
+#pragma unroll
+    for (int i = 1; i < 4; ++i) v = warp == 2 ? min(v, arr[1 + lane * 4 + i]) : max(v, arr[1 + lane * 4 + i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const int o = __shfl_xor_sync(0xffffffffu, v, d);
+      v = warp == 2 ? min(v, o) : max(v, o);
+    }
+    if (lane == 0) arr[0] = v;
+  }
   if (warp < 2) {  // inclusive scans of [1..128] by one warp each, 4 values per lane
     int* arr = warp == 0 ? scan : scan_k;
     int v[4];
@@ -489,7 +511,16 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
   const int64_t units_total = scan[kScanThreads];
   const int nonempty_total = scan_k[kScanThreads];
   const int64_t np_total = units_total - static_cast<int64_t>(p.piece_cost) * nonempty_total;
-  const int nteams_eff = effective_teams(p.nteams, np_total);
+  int nteams_eff = effective_teams(p.nteams, np_total);
+  // Sequences of one length whose count divides into about as many groups as there are teams: one
+  // team per group of k whole sequences.  Every piece is then a whole sequence — nothing is
+  // published, counted or merged — at the price of leaving up to a quarter of the CTA slots empty,
+  // which the streaming rate survives.
+  if (nonempty_total > 0 && scan_lo[0] == scan_hi[0]) {
+    const int k = (nonempty_total + p.nteams - 1) / p.nteams;   // sequences per team
+    const int groups = nonempty_total / k;
+    if (groups * k == nonempty_total && 4 * groups >= 3 * p.nteams) nteams_eff = groups;
+  }
   const bool any_empty = nonempty_total < p.batch;
 
   // Unit position x -> (sequence, page inside it, flat page index).  Positions inside a sequence's

@@ -337,3 +337,25 @@ def test_prefill_request_outside_the_table_is_skipped_and_reported():
         kernels.check_status(0)
     for r in (0, 1):
         assert _maxdiff(got[rows(r)], want[rows(r)]) <= ATTN_TOL
+
+
+@pytest.mark.parametrize("batch,kvh,length", [(64, 4, 290), (32, 8, 333), (74, 8, 160), (64, 8, 129), (37, 8, 33)])
+def test_uniform_lengths_take_whole_sequences_per_team(batch, kvh, length):
+    """Batches of one length are cut at sequence boundaries (one team per sequence, or per group of
+    k sequences): same numbers as ever.  With one odd sequence in the batch the general cut, with
+    its partial pieces and merges, is back."""
+    pages = batch * ((length + 17 + 15) // 16) + 8
+    for seed, odd in ((97, False), (98, True)):
+        lens = np.full(batch, length)
+        if odd:
+            lens[batch // 2] = length + 17
+        cfg = W.DecodeConfig("uniform", batch, 2 * kvh, kvh, pages, 1, 1, seed=seed)
+        c = W.make_decode_case(cfg, fill="hash", lengths=lens)
+        want_pool, want = _oracle_step(c)
+        for table_kind in ("block", "token"):
+            pool, out = _fused_gpu(c, table_kind)
+            torch.cuda.synchronize()
+            kernels.check_status(0)
+            assert torch.equal(pool.cpu(), want_pool)
+            assert _maxdiff(out, want) <= ATTN_TOL
+            assert _counters_are_zero()
