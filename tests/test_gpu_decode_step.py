@@ -339,10 +339,11 @@ def test_prefill_request_outside_the_table_is_skipped_and_reported():
         assert _maxdiff(got[rows(r)], want[rows(r)]) <= ATTN_TOL
 
 
-@pytest.mark.parametrize("batch,kvh,length", [(64, 4, 290), (32, 8, 333), (74, 8, 160), (64, 8, 129), (37, 8, 33)])
+@pytest.mark.parametrize("batch,kvh,length", [(64, 4, 290), (32, 8, 333), (74, 8, 160), (64, 8, 129), (37, 8, 33),
+                                                (16, 8, 500), (8, 4, 600), (5, 8, 300), (3, 1, 2000)])
 def test_uniform_lengths_take_whole_sequences_per_team(batch, kvh, length):
     """Batches of one length are cut at sequence boundaries (one team per sequence, or per group of
-    k sequences): same numbers as ever.  With one odd sequence in the batch the general cut, with
+    k sequences; with few sequences the general cut applies): same numbers as ever.  With one odd sequence in the batch the general cut, with
     its partial pieces and merges, is back."""
     pages = batch * ((length + 17 + 15) // 16) + 8
     for seed, odd in ((97, False), (98, True)):
