@@ -95,6 +95,13 @@ int b200kv_host_steps_flush(void* steps);
 /* Block until the slot's last submitted step has delivered its output to the host buffer. */
 int b200kv_host_steps_wait(void* steps, int slot);
 
+/*
+ * Wait for everything in flight and return the handle to its initial state (arrival counters of
+ * the split-KV workspace zeroed).  Needed only after the status word reported
+ * B200KV_DEV_WAIT_TIMEOUT: a launch that gave up on a wait may leave a counter short of wrapping.
+ */
+int b200kv_host_steps_reset(void* steps);
+
 /* The compute stream (a cudaStream_t), for a caller that orders other device work against the steps. */
 void* b200kv_host_steps_stream(void* steps);
 

@@ -135,6 +135,7 @@ _SIGNATURES = {
     "b200kv_host_steps_submit_bound": (c_int, [c_void_p, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
     "b200kv_host_steps_flush": (c_int, [c_void_p]),
     "b200kv_host_steps_wait": (c_int, [c_void_p, c_int]),
+    "b200kv_host_steps_reset": (c_int, [c_void_p]),
     "b200kv_host_steps_stream": (c_void_p, [c_void_p]),
 }
 

@@ -343,6 +343,22 @@ int b200kv_host_steps_wait(void* steps, int slot) {
   return B200KV_OK;
 }
 
+int b200kv_host_steps_reset(void* steps) {
+  using namespace b200kv;
+  HostSteps* h = static_cast<HostSteps*>(steps);
+  if (h == nullptr) return B200KV_EINVAL;
+  const int rc = launch_pending(*h);
+  HS_TRY(cudaStreamSynchronize(h->s_in));
+  HS_TRY(cudaStreamSynchronize(h->s_run));
+  HS_TRY(cudaStreamSynchronize(h->s_out));
+  for (int i = 0; i < h->depth; ++i) h->slot[i].idle = true;
+  // the arrival counters at the head of the workspace: a launch that gave up on a wait may have
+  // left some of them short of wrapping back to zero
+  HS_TRY(cudaMemsetAsync(h->workspace, 0, B200KV_DECODE_COUNTER_BYTES, h->s_run));
+  HS_TRY(cudaStreamSynchronize(h->s_run));
+  return rc;
+}
+
 void* b200kv_host_steps_stream(void* steps) {
   b200kv::HostSteps* h = static_cast<b200kv::HostSteps*>(steps);
   return h ? h->s_run : nullptr;

@@ -150,6 +150,13 @@ class HostDecodeSteps:
         if rc != 0:
             _lib.check(rc)
 
+    def reset(self) -> None:
+        """Wait for everything in flight and zero the workspace's arrival counters; needed only
+        after ``kernels.check_status`` reported a device-side wait that ran out (code 104)."""
+        rc = self._lib.b200kv_host_steps_reset(self._handle)
+        if rc != 0:
+            _lib.check(rc)
+
     @property
     def stream(self) -> torch.cuda.Stream:
         """The compute stream of the steps, to order other device work against them."""

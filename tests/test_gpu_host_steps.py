@@ -191,4 +191,13 @@ def test_unbound_submit_entry_point():
     with pytest.raises(ValueError):
         steps.submit(1, batch, bound, c.max_len)
     steps.wait(1)
+    # reset: nothing in flight afterwards, and the next step still gives the same numbers
+    steps.submit(0, batch, bound, c.max_len)
+    steps.reset()
+    got2 = torch.from_numpy(steps.buffers(0, batch).out.copy())
+    assert torch.equal(got2, got)
+    steps.submit(1, batch, bound, c.max_len)
+    steps.wait(1)
+    assert torch.equal(torch.from_numpy(steps.buffers(1, batch).out.copy()), got)
+    kernels.check_status(0)
     steps.close()

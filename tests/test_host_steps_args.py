@@ -24,6 +24,7 @@ def test_null_handle_is_an_argument_error(built_lib):
     lib = built_lib
     assert lib.b200kv_host_steps_wait(None, 0) == 1
     assert lib.b200kv_host_steps_flush(None) == 1
+    assert lib.b200kv_host_steps_reset(None) == 1
     assert lib.b200kv_host_steps_buffers(None, 0, 1, None, None, None, None, None, None) == 1
     assert lib.b200kv_host_steps_stream(None) is None
     lib.b200kv_host_steps_destroy(None)      # like free(NULL)
