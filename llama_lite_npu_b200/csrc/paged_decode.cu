@@ -423,7 +423,7 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
   float* merge_o = reinterpret_cast<float*>(smem + STAGES * kStageBytes);  // [4][128][ROWS]
   float* merge_ml = merge_o + kConsumerWarps * kD * ROWS;                  // [4][ROWS][2]
   uint64_t* bars = reinterpret_cast<uint64_t*>(merge_ml + kConsumerWarps * ROWS * 2);
-  int* arrival = reinterpret_cast<int*>(bars + 2 * STAGES);  // [2]: pieces to merge (0 = not last), first team
+  int* arrival = reinterpret_cast<int*>(bars + 2 * STAGES);  // [0] pieces to merge (0 = not the last arrival), [2] everybody else had arrived already
   int* scan = reinterpret_cast<int*>(merge_o);  // start-up only: [kScanThreads + 1] page prefix
 
   const int tid = threadIdx.x;
@@ -719,6 +719,7 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
   };
 
   bool alive = true;   // false once a wait of this warp ran out: keep walking, stop computing
+  unsigned seen_arrivals = 0;   // thread 0: the piece counter as seen at the start of a piece's last tile
   Tile t;
   for (int it = 0; cons.next(p, t); ++it) {
     if (t.first) {
@@ -744,6 +745,16 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
       }
     }
 
+    // Last tile of a partial piece: look at the sequence's arrival counter now (the answer is
+    // needed only after this tile's arithmetic).  If every other piece has already arrived, this
+    // CTA is going to be the one that merges, and its own hand-over needs neither the publishing
+    // fence nor the counter's round trip.
+    if (tid == 0 && t.last && !t.whole) {
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n"
+                   : "=r"(seen_arrivals)
+                   : "l"(p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head)
+                   : "memory");
+    }
     const int st = it % STAGES;
     if (alive && !mbar_wait_bounded(bar_full + 8 * st, (it / STAGES) & 1)) {
       set_status(p.status, B200KV_DEV_WAIT_TIMEOUT);
@@ -870,6 +881,17 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
               make_float2(o[j][nb][2], o[j][nb][3]);
         }
       }
+      // (thread 0, partial pieces) had every other piece of the sequence arrived when this piece's
+      // last tile began?  The flag rides on the barrier below.
+      const int64_t u0 = t.units0 + p.piece_cost;
+      const int t_first = team_of(u0, nteams_eff, units_total);
+      const int t_last = team_of(u0 + t.np - 1, nteams_eff, units_total);
+      const int npieces = t_last - t_first + 1;
+      if (tid == 0 && !t.whole) {
+        const bool others_in = seen_arrivals == static_cast<unsigned>(npieces - 1);
+        if (others_in) __threadfence();   // acquire: their published rows come before what follows
+        arrival[2] = others_in ? 1 : 0;
+      }
       consumer_bar();
       const int64_t slot = (static_cast<int64_t>(team) + t.b) * p.kv_heads + head;
       // Thread = output column; its ROWS values of a warp's O are contiguous in the merge buffer
@@ -926,26 +948,29 @@ paged_decode_kernel(DecodeParams p, const __grid_constant__ CUtensorMap kmap,
       if (!t.whole) {
         // A partial: publish it, count it, and merge the sequence if it was the last one to arrive.
         // The counter wraps to zero on the last arrival, so it needs no reset between launches.
-        __threadfence();
-        consumer_bar();
-        if (tid == 0) {
-          const int64_t u0 = t.units0 + p.piece_cost;
-          const int t_first = team_of(u0, nteams_eff, units_total);
-          const int t_last = team_of(u0 + t.np - 1, nteams_eff, units_total);
-          const int npieces = t_last - t_first + 1;
-          const unsigned old = atomicInc(p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head,
-                                         static_cast<unsigned>(npieces - 1));
-          const bool last_arrival = old == static_cast<unsigned>(npieces - 1);
-          arrival[0] = last_arrival ? npieces : 0;
-          arrival[1] = t_first;
-          // Acquire side of the hand-over, paid by the merging CTA only: this thread saw the other
-          // pieces' counts; the fence orders their published rows before everything that follows,
-          // and the named barrier below extends that to the other 127 threads.
-          if (last_arrival) __threadfence();
+        unsigned* ctr = p.piece_ctr + static_cast<int64_t>(t.b) * p.kv_heads + head;
+        if (arrival[2] != 0) {
+          // Everybody else had arrived before this piece's last tile: nobody waits for this
+          // partial but this CTA itself, which reads it back through L2 in the merge (a barrier,
+          // not a fence, orders that).  The count still has to wrap the counter to zero.
+          consumer_bar();
+          if (tid == 0) atomicInc(ctr, static_cast<unsigned>(npieces - 1));
+          merge_pieces<ROWS>(p, t.b, head, t_first, npieces, tid, merge_o, merge_ml);
+        } else {
+          __threadfence();
+          consumer_bar();
+          if (tid == 0) {
+            const unsigned old = atomicInc(ctr, static_cast<unsigned>(npieces - 1));
+            const bool last_arrival = old == static_cast<unsigned>(npieces - 1);
+            arrival[0] = last_arrival ? npieces : 0;
+            // Acquire side of the hand-over, paid by the merging CTA only: this thread saw the other
+            // pieces' counts; the fence orders their published rows before everything that follows,
+            // and the named barrier below extends that to the other 127 threads.
+            if (last_arrival) __threadfence();
+          }
+          consumer_bar();
+          if (arrival[0] > 0) merge_pieces<ROWS>(p, t.b, head, t_first, npieces, tid, merge_o, merge_ml);
         }
-        consumer_bar();
-        const int npieces = arrival[0];
-        if (npieces > 0) merge_pieces<ROWS>(p, t.b, head, arrival[1], npieces, tid, merge_o, merge_ml);
       }
     }
   }
