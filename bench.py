@@ -327,8 +327,10 @@ class Timer:
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         # A short device-side spin ahead of the start event: the host enqueues the graph launches
         # while it runs, so the events bracket K steps of device work and not the host's launch call.
-        with torch.cuda.stream(self.stream):
-            torch.cuda._sleep(60_000)
+        spin = getattr(torch.cuda, "_sleep", None)
+        if spin is not None:
+            with torch.cuda.stream(self.stream):
+                spin(60_000)
         t0.record(self.stream)
         for _ in range(full):
             g_full.replay()
