@@ -117,6 +117,7 @@ int build(HostSteps& h) {
     HS_TRY(cudaEventCreateWithFlags(&s.out_done, cudaEventDisableTiming));
   }
   h.workspace_bytes = decode_workspace_bytes(h.max_batch, h.q_heads, h.kv_heads, h.head_dim);
+  if (h.workspace_bytes == 0) return B200KV_ETOOLARGE;   // more (sequence, KV head) pairs than arrival counters
   HS_TRY(cudaMalloc(&h.workspace, h.workspace_bytes));
   // the piece counters at the head of the workspace start at zero and return to zero after a launch
   HS_TRY(cudaMemsetAsync(h.workspace, 0, h.workspace_bytes, h.s_run));
